@@ -1,1 +1,1 @@
-from . import llama  # noqa: F401  (registers the architecture)
+from . import llama, nibelorn  # noqa: F401  (registers the architectures)

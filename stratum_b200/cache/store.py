@@ -10,7 +10,7 @@ convolution/recurrent state per class (stratum/native/stratum_arch.h:53-67,
 
 Key/value storage of a group: K and V of shape
 [layers in group, pages, kv heads, PAGE_TOKENS, head size], so the rows of one
-(page, head) are contiguous.  State storage: [layers in group, slots, *shape].
+(page, head) are contiguous (V with heads and a size of its own where a mixer asks for that, or absent).  State storage: [layers in group, slots, *shape].
 """
 from __future__ import annotations
 
@@ -32,6 +32,18 @@ class KVSpec:
     head_dim: int
     window: int = 0
     key_order: str = "as_projected"
+    # values of another shape than the keys: `value_heads` heads of `value_dim` values per token (None: as the
+    # keys); value_heads = 0: no values are stored (a mixer whose values are a stretch of its key rows)
+    value_heads: Optional[int] = None
+    value_dim: Optional[int] = None
+
+    @property
+    def v_heads(self) -> int:
+        return self.n_kv_heads if self.value_heads is None else self.value_heads
+
+    @property
+    def v_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass(frozen=True)
@@ -108,7 +120,9 @@ class SequenceCache:
             if isinstance(g.spec, KVSpec):
                 shape = (n, self.n_pages, g.spec.n_kv_heads, PAGE_TOKENS, g.spec.head_dim)
                 g.k = torch.zeros(shape, dtype=self.dtype, device=self.device)
-                g.v = torch.zeros(shape, dtype=self.dtype, device=self.device)
+                if g.spec.v_heads > 0:
+                    shape_v = (n, self.n_pages, g.spec.v_heads, PAGE_TOKENS, g.spec.v_dim)
+                    g.v = torch.zeros(shape_v, dtype=self.dtype, device=self.device)
             else:
                 dt = torch.float32 if g.spec.dtype == "float32" else self.dtype
                 # one row more than there are slots: row `max_seqs` belongs to no sequence; the padding rows of a
@@ -222,6 +236,6 @@ class SequenceCache:
         gi, idx = self.layer_group[layer]
         g = self.groups[gi]
         if isinstance(g.spec, KVSpec):
-            return LayerCache(spec=g.spec, writes=writes, k=g.k[idx], v=g.v[idx],
+            return LayerCache(spec=g.spec, writes=writes, k=g.k[idx], v=None if g.v is None else g.v[idx],
                               block_table=block_tables.get(gi))
         return LayerCache(spec=g.spec, writes=writes, state=g.state[idx])

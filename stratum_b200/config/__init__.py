@@ -1,8 +1,9 @@
 from .base import ConfigError, KeyReader, ModelConfig, read_config_json
 from .llama import LlamaConfig, RopeScaling
+from .nibelorn import NibelornConfig
 from .registry import (Architecture, architecture_name, find_architecture, register_architecture,
                        registered_architectures)
 
-__all__ = ["ConfigError", "KeyReader", "ModelConfig", "read_config_json", "LlamaConfig", "RopeScaling",
+__all__ = ["ConfigError", "KeyReader", "ModelConfig", "read_config_json", "LlamaConfig", "RopeScaling", "NibelornConfig",
            "Architecture", "architecture_name", "find_architecture", "register_architecture",
            "registered_architectures"]

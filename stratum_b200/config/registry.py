@@ -47,10 +47,11 @@ def architecture_name(raw: Dict[str, Any]) -> str:
     archs = raw.get("architectures")
     if isinstance(archs, list) and archs and isinstance(archs[0], str):
         return archs[0]
-    mt = raw.get("model_type")
-    if isinstance(mt, str):
-        return mt
-    raise ConfigError("config.json: neither 'architectures' nor 'model_type' names the model")
+    for key in ("architecture", "model_type"):
+        name = raw.get(key)
+        if isinstance(name, str):
+            return name
+    raise ConfigError("config.json: none of 'architectures', 'architecture' and 'model_type' names the model")
 
 
 def find_architecture(raw_or_name) -> Architecture:

@@ -1,4 +1,4 @@
-// Embedding gather, RMSNorm, SwiGLU and rotary position encoding fused with the cache write.
+// Embedding gather, RMSNorm, Dynamic Tanh, SwiGLU, GELU and rotary position encoding fused with the cache write.
 //
 // The residual stream is float32 on every path; T is the dtype of weights, of the
 // normed activations that feed matrix products, and of the cache (float or bfloat16).
@@ -179,6 +179,68 @@ STRATUM_EXPORT int stratum_rmsnorm_heads(void* x, int dtype, int n_rows, int str
     return launch_pdl(rmsnorm_heads_kernel<bf16>, blocks, warps * 32, 0, stream, (bf16*)x, n_rows, stride, first_col,
                       n_heads, head_dim, gain, eps);
   return STRATUM_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------- Dynamic Tanh
+// y = tanh(alpha * x) * w + b: a norm without mean or variance; alpha is one learned number, read from the
+// device.  x float32 [*, hidden]; row r of the output reads row rows[r] of x when rows != nullptr.
+template <typename T>
+__global__ void dynamic_tanh_kernel(const float* __restrict__ x, const float* __restrict__ alpha,
+                                    const float* __restrict__ w, const float* __restrict__ b,
+                                    const int* __restrict__ rows, T* __restrict__ out, int hidden) {
+  pdl_trigger();
+  const float a = alpha[0];
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  const float* xr = x + (size_t)src * hidden;
+  T* o = out + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    o[i] = from_float<T>(fmaf(tanhf(a * ld_fresh(xr + i)), w[i], b[i]));
+}
+
+STRATUM_EXPORT int stratum_dynamic_tanh(const float* x, const float* alpha, const float* w, const float* b,
+                                        const int* rows, void* out, int out_dtype, int n_rows, int hidden,
+                                        cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  if (out_dtype == STRATUM_DT_F32)
+    return launch_pdl(dynamic_tanh_kernel<float>, n_rows, threads, 0, stream, x, alpha, w, b, rows, (float*)out, hidden);
+  if (out_dtype == STRATUM_DT_BF16)
+    return launch_pdl(dynamic_tanh_kernel<bf16>, n_rows, threads, 0, stream, x, alpha, w, b, rows, (bf16*)out, hidden);
+  return STRATUM_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------- GELU
+// In place over [rows][ld], the first `width` columns of every row.
+// kind 0: z * 0.5 * (1 + erf(z / sqrt 2));  kind 1: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+__device__ __forceinline__ float gelu_value(float z, int kind) {
+  if (kind == 0) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
+  return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename T>
+__global__ void gelu_kernel(T* __restrict__ x, int width, int ld, size_t total, int kind) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t r = i / width;
+  T* p = x + r * ld + (i - r * width);
+  *p = from_float<T>(gelu_value(to_float(*p), kind));
+}
+
+STRATUM_EXPORT int stratum_gelu(void* x, int dtype, int n_rows, int width, int ld, int kind, cudaStream_t stream) {
+  const size_t total = (size_t)n_rows * width;
+  if (total == 0) return 0;
+  if (kind != 0 && kind != 1) return STRATUM_ERR_SHAPE;
+  const int threads = 256;
+  const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+  if (dtype == STRATUM_DT_F32)
+    gelu_kernel<float><<<blocks, threads, 0, stream>>>((float*)x, width, ld, total, kind);
+  else if (dtype == STRATUM_DT_BF16)
+    gelu_kernel<bf16><<<blocks, threads, 0, stream>>>((bf16*)x, width, ld, total, kind);
+  else
+    return STRATUM_ERR_DTYPE;
+  return launch_status();
 }
 
 // ---------------------------------------------------------------- SwiGLU

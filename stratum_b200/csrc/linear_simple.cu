@@ -20,10 +20,15 @@
 template <typename T, int EPI>
 __global__ void __launch_bounds__(256)
 linear_simple_kernel(const T* __restrict__ x, const T* __restrict__ w, const float* __restrict__ bias,
-                     void* __restrict__ out, int M, int N, int K, int ldx, int ldo) {
+                     void* __restrict__ out, int M, int N, int K, int ldx, int ldo, int x_step, long long w_step,
+                     int o_step) {
   __shared__ float xs[LS_BK][LS_BM + 1];
   __shared__ float ws[LS_BK][LS_BN + 1];
   const int tid = threadIdx.x;
+  // one product per blockIdx.z (the heads of linear_heads): operands and result move on by their steps
+  x += (size_t)blockIdx.z * x_step;
+  w += (size_t)blockIdx.z * w_step;
+  const size_t o_shift = (size_t)blockIdx.z * o_step;
   const int m0 = blockIdx.y * LS_BM, n0 = blockIdx.x * LS_BN;
   const int tm = (tid / 16) * LS_TM, tn = (tid % 16) * LS_TN;
   float acc[LS_TM][LS_TN];
@@ -67,7 +72,7 @@ linear_simple_kernel(const T* __restrict__ x, const T* __restrict__ w, const flo
       if (n >= N) continue;
       float v = acc[i][j];
       if (bias) v += bias[n];
-      const size_t o = (size_t)m * ldo + n;
+      const size_t o = (size_t)m * ldo + n + o_shift;
       if (EPI == 0) ((T*)out)[o] = from_float<T>(v);
       else if (EPI == 1) ((float*)out)[o] += v;
       else ((float*)out)[o] = v;
@@ -77,14 +82,18 @@ linear_simple_kernel(const T* __restrict__ x, const T* __restrict__ w, const flo
 
 template <typename T>
 static int launch_linear_simple(const void* x, const void* w, const float* bias, void* out, int epilogue,
-                                int M, int N, int K, int ldx, int ldo, cudaStream_t stream) {
-  dim3 grid((N + LS_BN - 1) / LS_BN, (M + LS_BM - 1) / LS_BM);
+                                int M, int N, int K, int ldx, int ldo, cudaStream_t stream, int heads = 1,
+                                int x_step = 0, long long w_step = 0, int o_step = 0) {
+  dim3 grid((N + LS_BN - 1) / LS_BN, (M + LS_BM - 1) / LS_BM, heads);
   if (epilogue == 0)
-    linear_simple_kernel<T, 0><<<grid, 256, 0, stream>>>((const T*)x, (const T*)w, bias, out, M, N, K, ldx, ldo);
+    linear_simple_kernel<T, 0><<<grid, 256, 0, stream>>>((const T*)x, (const T*)w, bias, out, M, N, K, ldx, ldo,
+                                                      x_step, w_step, o_step);
   else if (epilogue == 1)
-    linear_simple_kernel<T, 1><<<grid, 256, 0, stream>>>((const T*)x, (const T*)w, bias, out, M, N, K, ldx, ldo);
+    linear_simple_kernel<T, 1><<<grid, 256, 0, stream>>>((const T*)x, (const T*)w, bias, out, M, N, K, ldx, ldo,
+                                                      x_step, w_step, o_step);
   else if (epilogue == 2)
-    linear_simple_kernel<T, 2><<<grid, 256, 0, stream>>>((const T*)x, (const T*)w, bias, out, M, N, K, ldx, ldo);
+    linear_simple_kernel<T, 2><<<grid, 256, 0, stream>>>((const T*)x, (const T*)w, bias, out, M, N, K, ldx, ldo,
+                                                      x_step, w_step, o_step);
   else
     return STRATUM_ERR_SHAPE;
   return launch_status();
@@ -99,5 +108,25 @@ STRATUM_EXPORT int stratum_linear_simple(const void* x, const void* w, const flo
   if ((M + LS_BM - 1) / LS_BM > 65535) return STRATUM_ERR_LIMIT;
   if (dtype == STRATUM_DT_F32) return launch_linear_simple<float>(x, w, bias, out, epilogue, M, N, K, ldx, ldo, stream);
   if (dtype == STRATUM_DT_BF16) return launch_linear_simple<bf16>(x, w, bias, out, epilogue, M, N, K, ldx, ldo, stream);
+  return STRATUM_ERR_DTYPE;
+}
+
+// The same product once per head: head j multiplies columns [j * x_step, j * x_step + K) of x by the matrix
+// w[j] ([heads][N][K]) into columns [j * o_step, j * o_step + N) of out.  No bias.
+STRATUM_EXPORT int stratum_linear_heads(const void* x, const void* w, void* out, int dtype, int epilogue, int heads,
+                                        int M, int N, int K, int ldx, int ldo, int x_step, int o_step,
+                                        cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || heads <= 0) return 0;
+  if (K <= 0 || x_step < 0 || o_step < 0 || (long long)(heads - 1) * x_step + K > ldx ||
+      (long long)(heads - 1) * o_step + N > ldo)
+    return STRATUM_ERR_SHAPE;
+  if ((M + LS_BM - 1) / LS_BM > 65535 || heads > 65535) return STRATUM_ERR_LIMIT;
+  const long long w_step = (long long)N * K;
+  if (dtype == STRATUM_DT_F32)
+    return launch_linear_simple<float>(x, w, nullptr, out, epilogue, M, N, K, ldx, ldo, stream, heads, x_step, w_step,
+                                       o_step);
+  if (dtype == STRATUM_DT_BF16)
+    return launch_linear_simple<bf16>(x, w, nullptr, out, epilogue, M, N, K, ldx, ldo, stream, heads, x_step, w_step,
+                                      o_step);
   return STRATUM_ERR_DTYPE;
 }

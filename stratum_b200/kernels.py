@@ -183,6 +183,39 @@ def rmsnorm_heads(x: torch.Tensor, first_col: int, n_heads: int, head_dim: int, 
              c_float(eps), _stream()), "rmsnorm_heads")
 
 
+def dynamic_tanh(x: torch.Tensor, alpha: torch.Tensor, w: torch.Tensor, b: torch.Tensor, out: torch.Tensor,
+                 rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = tanh(alpha * x[rows[r]] or x[r]) * w + b.  x float32 [*,H]; alpha float32 (one number, on the
+    device); w, b float32 [H]."""
+    _need(x, "x", torch.float32); _need(alpha, "alpha", torch.float32); _need(w, "w", torch.float32)
+    _need(b, "b", torch.float32); _need(out, "out")
+    n_rows = out.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        if rows.numel() != n_rows:
+            raise KernelError("dynamic_tanh: rows and out disagree")
+    elif x.shape[0] != n_rows:
+        raise KernelError("dynamic_tanh: x and out disagree")
+    if alpha.numel() != 1 or w.numel() != x.shape[-1] or b.numel() != x.shape[-1]:
+        raise KernelError("dynamic_tanh: alpha is one number, w and b have the row's length")
+    f = _fn("elementwise", "stratum_dynamic_tanh",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(alpha), _ptr(w), _ptr(b), _ptr(rows), _ptr(out), dtype_code(out.dtype), n_rows,
+             x.shape[-1], _stream()), "dynamic_tanh")
+
+
+GELU_ERF, GELU_TANH = 0, 1
+
+
+def gelu(x: torch.Tensor, kind: int = GELU_ERF) -> None:
+    """In place over the rows of x [rows, width]: the exact GELU (kind GELU_ERF) or its tanh form (GELU_TANH)."""
+    _need(x, "x", contiguous=False)
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("gelu: rows must be contiguous")
+    f = _fn("elementwise", "stratum_gelu", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), dtype_code(x.dtype), x.shape[0], x.shape[1], x.stride(0), kind, _stream()), "gelu")
+
+
 def swiglu(gu: torch.Tensor, out: torch.Tensor) -> None:
     """out[r][j] = silu(gu[r][2j]) * gu[r][2j+1]."""
     _need(gu, "gu"); _need(out, "out", gu.dtype)
@@ -257,6 +290,20 @@ def linear_simple(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
     _check(f(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), dtype_code(x.dtype), epilogue, M, N, K, x.stride(0),
              out.stride(0), _stream()), "linear_simple")
+
+
+def linear_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_step: int, o_step: int) -> None:
+    """One product per head on the CUDA cores: out[:, j*o_step : j*o_step+N] = x[:, j*x_step : j*x_step+K] @ w[j].T.
+    x [M, >= (heads-1)*x_step+K] and w [heads, N, K] of one dtype, out of the same dtype."""
+    _need(x, "x", contiguous=False); _need(w, "w", x.dtype); _need(out, "out", x.dtype, contiguous=False)
+    if x.stride(-1) != 1 or out.stride(-1) != 1 or w.dim() != 3:
+        raise KernelError("linear_heads: rows must be contiguous and w [heads, N, K]")
+    heads, N, Kd = w.shape
+    f = _fn("linear_simple", "stratum_linear_heads",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_void_p])
+    _check(f(_ptr(x), _ptr(w), _ptr(out), dtype_code(x.dtype), EPI_STORE, heads, x.shape[0], N, Kd, x.stride(0),
+             out.stride(0), x_step, o_step, _stream()), "linear_heads")
 
 
 def _linear_shapes(x, w, bias, out, epilogue, what):
@@ -447,6 +494,131 @@ def attention_simple(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
     _check(f(_ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), dtype_code(qkv.dtype), _ptr(token_pos),
              _ptr(token_seq), _ptr(block_table), block_table.stride(0), _ptr(out), out.stride(0), qkv.shape[0],
              n_q, n_kv, head_dim, page_tokens, window, c_float(scale), _stream()), "attention_simple")
+
+
+class _MixerPrep(ctypes.Structure):
+    """Mirror of struct MixerPrep in csrc/mixer_prep.cu."""
+    _fields_ = [("x", c_void_p), ("token_pos", c_void_p), ("token_seq", c_void_p), ("block_table", c_void_p),
+                ("inv_freq", c_void_p), ("k_norm_gain", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p),
+                ("q_out", c_void_p), ("ld", c_int), ("bt_stride", c_int), ("n_tokens", c_int), ("rot_pairs", c_int),
+                ("n_q", c_int), ("q_dim", c_int), ("q_col", c_int), ("q_rot_off", c_int),
+                ("n_k", c_int), ("k_dim", c_int), ("k_col", c_int), ("k_rot_off", c_int), ("k_norm_n", c_int),
+                ("n_v", c_int), ("v_dim", c_int), ("v_col", c_int),
+                ("page_tokens", c_int), ("write_cache", c_int), ("eps", c_float),
+                ("q_out_ld", c_int), ("q_out_step", c_int), ("q_out_off", c_int)]
+
+
+def mixer_prep(x: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor, block_table: Optional[torch.Tensor],
+               k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], page_tokens: int, write_cache: bool,
+               *, queries=(0, 0, 0), keys=(0, 0, 0), values=(0, 0, 0), inv_freq: Optional[torch.Tensor] = None,
+               q_rot_off: int = 0, k_rot_off: int = 0, k_norm_gain: Optional[torch.Tensor] = None,
+               eps: float = 0.0, q_out: Optional[torch.Tensor] = None, q_out_step: int = 0,
+               q_out_off: int = 0) -> None:
+    """Between a fused projection and attention.  x [tokens, ld] holds runs of equal heads: queries, keys, values,
+    each given as (heads, head size, first column).  Queries: dimensions [q_rot_off, q_rot_off + 2R) rotated in
+    place (R = len(inv_freq), pairs (i, i + R)); with q_out [tokens, *] the dimensions from q_rot_off on go, the
+    first 2R rotated, to q_out[:, j * q_out_step + q_out_off ...] for head j instead.  Keys: the first len(k_norm_gain) dimensions divided by their
+    root mean square (eps inside the root) times the gain, dimensions [k_rot_off, k_rot_off + 2R) rotated, then
+    appended to k_cache.  Values: appended to v_cache.  Tokens of no sequence are left alone."""
+    _need(x, "x", contiguous=False); _need(token_pos, "token_pos", torch.int32)
+    _need(token_seq, "token_seq", torch.int32)
+    p = _MixerPrep()
+    p.x, p.token_pos, p.token_seq = x.data_ptr(), token_pos.data_ptr(), token_seq.data_ptr()
+    p.ld, p.n_tokens = x.stride(0), x.shape[0]
+    p.n_q, p.q_dim, p.q_col = queries
+    p.n_k, p.k_dim, p.k_col = keys
+    p.n_v, p.v_dim, p.v_col = values
+    p.q_rot_off, p.k_rot_off = q_rot_off, k_rot_off
+    if inv_freq is not None:
+        _need(inv_freq, "inv_freq", torch.float32)
+        p.inv_freq, p.rot_pairs = inv_freq.data_ptr(), inv_freq.numel()
+    if k_norm_gain is not None:
+        _need(k_norm_gain, "k_norm_gain", torch.float32)
+        p.k_norm_gain, p.k_norm_n = k_norm_gain.data_ptr(), k_norm_gain.numel()
+    p.eps, p.page_tokens, p.write_cache = float(eps), page_tokens, int(bool(write_cache))
+    if q_out is not None:
+        _need(q_out, "q_out", x.dtype, contiguous=False)
+        p.q_out, p.q_out_ld, p.q_out_step, p.q_out_off = q_out.data_ptr(), q_out.stride(0), q_out_step, q_out_off
+    if write_cache:
+        _need(block_table, "block_table", torch.int32, contiguous=False)
+        p.block_table, p.bt_stride = block_table.data_ptr(), block_table.stride(0)
+        if p.n_k:
+            _need(k_cache, "k_cache", x.dtype)
+            p.k_cache = k_cache.data_ptr()
+        if p.n_v:
+            _need(v_cache, "v_cache", x.dtype)
+            p.v_cache = v_cache.data_ptr()
+    f = _fn("mixer_prep", "stratum_mixer_prep", [c_void_p, c_int, c_void_p])
+    _check(f(ctypes.addressof(p), dtype_code(x.dtype), _stream()), "mixer_prep")
+
+
+class _GeneralAttention(ctypes.Structure):
+    """Mirror of struct GeneralAttention in csrc/attention_general.h."""
+    _fields_ = [("q", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p), ("out", c_void_p),
+                ("token_pos", c_void_p), ("token_seq", c_void_p), ("block_table", c_void_p),
+                ("qb_seq", c_void_p), ("qb_tok0", c_void_p), ("qb_ntok", c_void_p),
+                ("part_o", c_void_p), ("part_ml", c_void_p),
+                ("ldq", c_int), ("ldo", c_int), ("bt_stride", c_int), ("n_tokens", c_int),
+                ("n_heads", c_int), ("group", c_int), ("maps", c_int),
+                ("qk_dim", c_int), ("v_dim", c_int), ("n_k_heads", c_int), ("n_v_heads", c_int), ("v_in_k", c_int),
+                ("page_tokens", c_int), ("window", c_int), ("combine", c_int), ("gate_col", c_int),
+                ("temp_every", c_int), ("n_qblocks", c_int), ("tokens_per_block", c_int), ("n_splits", c_int),
+                ("chunk", c_int), ("reserved", c_int),
+                ("scale", c_float), ("softcap", c_float), ("temp_coef", c_float), ("lam", c_float),
+                ("out_scale", c_float), ("eps", c_float)]
+
+
+class AttentionShape:
+    """The constants of a general attention (see csrc/attention_general.cu): heads, query heads per key/value
+    head (`group`), score maps per head, key and value sizes, whether the values are the first v_dim values of
+    the key rows, scale, softcap (0: none), window (0: every key), the query factor
+    1 + temp_coef ln(floor((p + 1) / temp_every) + 1), and for two maps the combination
+    (a_0 - lam a_1) / rms * out_scale with its eps and the column of the output gate (-1: none)."""
+
+    def __init__(self, n_heads: int, group: int, maps: int, qk_dim: int, v_dim: int, v_in_k: bool, scale: float,
+                 softcap: float = 0.0, window: int = 0, temp_coef: float = 0.0, temp_every: int = 1,
+                 lam: float = 0.0, out_scale: float = 1.0, eps: float = 0.0, gate_col: int = -1):
+        self.n_heads, self.group, self.maps, self.qk_dim, self.v_dim = n_heads, group, maps, qk_dim, v_dim
+        self.v_in_k, self.scale, self.softcap, self.window = bool(v_in_k), scale, softcap, window
+        self.temp_coef, self.temp_every, self.lam, self.out_scale = temp_coef, temp_every, lam, out_scale
+        self.eps, self.gate_col = eps, gate_col
+
+    def fill(self, p: "_GeneralAttention") -> None:
+        p.n_heads, p.group, p.maps, p.qk_dim, p.v_dim = self.n_heads, self.group, self.maps, self.qk_dim, self.v_dim
+        p.n_k_heads = (self.n_heads // self.group) * self.maps
+        p.n_v_heads = 0 if self.v_in_k else self.n_heads // self.group
+        p.v_in_k, p.window, p.combine, p.gate_col = int(self.v_in_k), self.window, int(self.maps == 2), self.gate_col
+        p.temp_every, p.scale, p.softcap, p.temp_coef = self.temp_every, self.scale, self.softcap, self.temp_coef
+        p.lam, p.out_scale, p.eps = self.lam, self.out_scale, self.eps
+
+
+def _general_params(shape: AttentionShape, q, k_cache, v_cache, token_pos, token_seq, block_table, out,
+                    page_tokens: int) -> "_GeneralAttention":
+    _need(q, "q", contiguous=False); _need(k_cache, "k_cache", q.dtype); _need(out, "out", q.dtype, contiguous=False)
+    _need(token_pos, "token_pos", torch.int32); _need(token_seq, "token_seq", torch.int32)
+    _need(block_table, "block_table", torch.int32, contiguous=False)
+    if q.stride(-1) != 1 or out.stride(-1) != 1:
+        raise KernelError("attention_general: rows must be contiguous")
+    p = _GeneralAttention()
+    shape.fill(p)
+    p.q, p.k_cache, p.out = q.data_ptr(), k_cache.data_ptr(), out.data_ptr()
+    if not shape.v_in_k:
+        _need(v_cache, "v_cache", q.dtype)
+        p.v_cache = v_cache.data_ptr()
+    p.token_pos, p.token_seq, p.block_table = token_pos.data_ptr(), token_seq.data_ptr(), block_table.data_ptr()
+    p.ldq, p.ldo, p.bt_stride, p.n_tokens, p.page_tokens = q.stride(0), out.stride(0), block_table.stride(0), \
+        q.shape[0], page_tokens
+    return p
+
+
+def attention_general(shape: AttentionShape, q: torch.Tensor, k_cache: torch.Tensor, v_cache: Optional[torch.Tensor],
+                      token_pos: torch.Tensor, token_seq: torch.Tensor, block_table: torch.Tensor, out: torch.Tensor,
+                      page_tokens: int) -> None:
+    """Causal attention of every token of the step over its sequence's cached keys for the shapes AttentionShape
+    describes, on the CUDA cores in float32 (q, the cache and out in one dtype)."""
+    p = _general_params(shape, q, k_cache, v_cache, token_pos, token_seq, block_table, out, page_tokens)
+    f = _fn("attention_general", "stratum_attention_general", [c_void_p, c_int, c_void_p])
+    _check(f(ctypes.addressof(p), dtype_code(q.dtype), _stream()), "attention_general")
 
 
 def attention_mma(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, token_pos: torch.Tensor,

@@ -1,4 +1,4 @@
-from . import attention, block, embedding, mlp, norm, rope  # noqa: F401  (registers the built-in parts)
+from . import attention, block, differential_attention, embedding, latent_attention, mlp, norm, rope  # noqa: F401  (registers the built-in parts)
 from .base import (Arrangement, Embedding, FeedForward, Head, Mixer, Norm, Part, PositionEncoding,
                    RotaryTable, Runtime)
 from .registry import find_part, register_part, registered

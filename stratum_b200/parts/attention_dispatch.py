@@ -80,3 +80,10 @@ def run(att, qkv: torch.Tensor, cache, step, out: torch.Tensor) -> None:
         K.attention_tile(qkv, cache.k, cache.v, step.token_pos, step.token_seq, cache.block_table,
                          step.query_blocks(4 * per_warp), per_warp, out, att.n_heads, att.n_kv_heads, hd,
                          PAGE_TOKENS, att.window, att.scale)
+
+
+def run_general(att, shape, q: torch.Tensor, cache, step, out: torch.Tensor) -> None:
+    """Attention of the shapes kernels.AttentionShape describes (key and value sizes of their own, values inside the
+    key rows, several maps per head): q [tokens, *] holds head j's map m at column (j * maps + m) * qk_dim."""
+    K.attention_general(shape, q, cache.k, cache.v, step.token_pos, step.token_seq, cache.block_table, out,
+                        PAGE_TOKENS)

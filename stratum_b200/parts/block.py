@@ -15,6 +15,7 @@ class PreNormResidual(Arrangement):
     replays_prompts = True
 
     slots = {"mixer_norm": "norm", "mixer": "mixer", "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
+    optional = ("feed_forward_norm", "feed_forward")       # a layer may be a mixer alone
     carries = True
 
     def accepts_carry(self, layer):
@@ -27,6 +28,9 @@ class PreNormResidual(Arrangement):
         norm_a, mixer = layer.part("mixer_norm"), layer.part("mixer")
         norm_b, ff = layer.part("feed_forward_norm"), layer.part("feed_forward")
         xn = carry if carry is not None else norm_a.forward(x)
+        if ff is None or norm_b is None:
+            mixer.forward(xn, x, step, cache)
+            return None
         ask = norm_b.handover() if mixer.hands_on and ff.takes_normed_rows else None
         if ask is not None:
             mixer.forward(xn, x, step, cache, emit=ask)

@@ -16,19 +16,21 @@ from .spec import TensorSpec
 
 @register_part("embedding", "token_embedding")
 class TokenEmbedding(Embedding):
-    """params: vocab, hidden, prefix (e.g. "model.embed_tokens.")."""
+    """params: vocab, hidden, prefix (e.g. "model.embed_tokens."; the table is prefix + "weight"), or tensor (the
+    table's whole name)."""
     replays_prompts = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.vocab, self.hidden = int(spec["vocab"]), int(spec["hidden"])
+        self.name = spec.get("tensor") or self.prefix + "weight"
         self._table: Optional[torch.Tensor] = None
 
     def tensors(self) -> Dict[str, TensorSpec]:
-        return {self.prefix + "weight": TensorSpec((self.vocab, self.hidden))}
+        return {self.name: TensorSpec((self.vocab, self.hidden))}
 
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
-        self._table = weights[self.prefix + "weight"]
+        self._table = weights[self.name]
 
     def table(self) -> torch.Tensor:
         return self._table
@@ -41,20 +43,22 @@ class TokenEmbedding(Embedding):
 
 @register_part("head", "linear_head")
 class LinearHead(Head):
-    """params: vocab, hidden, tied (the file may leave the matrix out), prefix (e.g. "lm_head.")."""
+    """params: vocab, hidden, tied (the file may leave the matrix out), prefix (e.g. "lm_head."; the matrix is
+    prefix + "weight"), or tensor (the matrix's whole name)."""
     replays_prompts = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.vocab, self.hidden = int(spec["vocab"]), int(spec["hidden"])
         self.tied = bool(spec.get("tied", False))
+        self.name = spec.get("tensor") or self.prefix + "weight"
         self.proj: Optional[Linear] = None
 
     def tensors(self) -> Dict[str, TensorSpec]:
-        return {self.prefix + "weight": TensorSpec((self.vocab, self.hidden), optional=self.tied)}
+        return {self.name: TensorSpec((self.vocab, self.hidden), optional=self.tied)}
 
     def bind_with_embedding(self, weights: Mapping[str, torch.Tensor], table: torch.Tensor) -> None:
-        w = weights.get(self.prefix + "weight")
+        w = weights.get(self.name)
         self.proj = Linear(self.runtime, w if w is not None else table)
 
     def forward(self, xn: torch.Tensor) -> torch.Tensor:

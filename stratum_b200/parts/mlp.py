@@ -1,4 +1,6 @@
-"""SwiGLU feed-forward: residual += Wd (silu(Wg xn) * (Wu xn))
+"""Feed-forwards.
+Dense with a GELU: residual += Wd gelu(Wu xn), the exact (erf) GELU or its tanh form.
+SwiGLU feed-forward: residual += Wd (silu(Wg xn) * (Wu xn))
 (stratum/native/stratum_arch_llama.inc.c:550-555, stratum/native/stratum_engine.h:373-391).
 
 Gate and up run as one matrix product over a weight whose rows alternate gate_j, up_j, so that
@@ -11,7 +13,8 @@ from typing import Dict, Mapping, Optional
 import torch
 
 from .base import FeedForward
-from .linear import ADD_TO_F32, SWIGLU, Linear
+from .. import kernels as K
+from .linear import ADD_TO_F32, STORE, SWIGLU, Linear
 from .registry import register_part
 from .spec import TensorSpec
 
@@ -56,3 +59,35 @@ class SwiGLU(FeedForward):
     def forward(self, xn, residual: torch.Tensor, step, emit=None) -> None:
         a = self.gate_up(xn, mode=SWIGLU)
         self.down(a, out=residual, mode=ADD_TO_F32, emit=emit)
+
+
+@register_part("feed_forward", "dense_gelu")
+class DenseGelu(FeedForward):
+    """params: hidden, intermediate, activation ("gelu_erf" | "gelu_tanh"), up / down (tensor names), prefix."""
+    replays_prompts = True
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.hidden = int(spec["hidden"])
+        self.intermediate = int(spec["intermediate"])
+        act = spec.get("activation", "gelu_erf")
+        if act not in ("gelu_erf", "gelu_tanh"):
+            raise ValueError(f"dense_gelu: activation {act!r} is neither gelu_erf nor gelu_tanh")
+        self.kind = K.GELU_ERF if act == "gelu_erf" else K.GELU_TANH
+        self.up_name = self.prefix + spec.get("up", "up")
+        self.down_name = self.prefix + spec.get("down", "down")
+        self.up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        return {self.up_name: TensorSpec((self.intermediate, self.hidden)),
+                self.down_name: TensorSpec((self.hidden, self.intermediate))}
+
+    def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
+        self.up = Linear(self.runtime, weights[self.up_name])
+        self.down = Linear(self.runtime, weights[self.down_name])
+
+    def forward(self, xn, residual: torch.Tensor, step) -> None:
+        a = self.up(xn, mode=STORE)
+        K.gelu(a, self.kind)
+        self.down(a, out=residual, mode=ADD_TO_F32)

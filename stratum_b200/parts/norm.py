@@ -1,4 +1,6 @@
-"""RMSNorm: y = x / sqrt(mean(x^2) + eps) * gain  (stratum/native/stratum_arch_llama.inc.c:45-76)."""
+"""Norms on the residual stream.
+RMSNorm: y = x / sqrt(mean(x^2) + eps) * gain  (stratum/native/stratum_arch_llama.inc.c:45-76).
+Dynamic Tanh: y = tanh(alpha x) * w + b, which computes no mean and no variance."""
 from __future__ import annotations
 
 from typing import Dict, Mapping, Optional
@@ -44,3 +46,30 @@ class RMSNorm(Norm):
         if head_dim != self.size:
             raise ValueError(f"rmsnorm of size {self.size} asked to normalise heads of {head_dim}")
         K.rmsnorm_heads(x, first_col, n_heads, head_dim, self.gain, self.eps)
+
+
+@register_part("norm", "dynamic_tanh")
+class DynamicTanh(Norm):
+    """params: size, name (the weight's tensor name; the bias is name + ".b", the scalar name + ".alpha")."""
+    replays_prompts = True
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.size = int(spec["size"])
+        self.name = str(spec["name"])
+        self.w = self.b = self.alpha = None
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        return {self.name: TensorSpec((self.size,), role="vector", init="ones"),
+                self.name + ".b": TensorSpec((self.size,), role="vector", init="zeros"),
+                self.name + ".alpha": TensorSpec((), role="vector", init="ones")}
+
+    def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
+        self.w, self.b = weights[self.name], weights[self.name + ".b"]
+        self.alpha = weights[self.name + ".alpha"].reshape(1)
+
+    def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        n = x.shape[0] if rows is None else rows.numel()
+        out = self.runtime.empty(n, self.size)
+        K.dynamic_tanh(x, self.alpha, self.w, self.b, out, rows)
+        return out
