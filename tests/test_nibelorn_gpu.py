@@ -1,0 +1,287 @@
+"""Nibelorn on the GPU against the plain implementation: each mechanism alone, whole prompts against token-by-token
+decoding, prompts fed in portions, unequal batches, pages and slots used again, keys far back and at page borders,
+the first tokens, long decoding, generation through the entry point."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import TOL, assert_close, rand_tokens
+from nibelorn_helpers import CONFIGS, make, plain_logits
+from plain import nibelorn_plain as N
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+
+
+def _engine(path, dtype, max_tokens=1024):
+    from stratum_b200.engine import Engine, load_model
+    model, _ = load_model(path, torch.float32 if dtype == "float32" else torch.bfloat16, "cuda")
+    return Engine(model, max_tokens=max_tokens)
+
+
+@pytest.fixture(scope="module", params=[(n, d) for n in ("A", "B", "TC") for d in DTYPES], ids=lambda p: f"{p[0]}-{p[1]}")
+def setup(request, tmp_path_factory):
+    name, dtype = request.param
+    path, cfg, w = make(str(tmp_path_factory.mktemp(f"nib{name}_{dtype}")), name, dtype, seed=len(name) + 1)
+    return name, dtype, cfg, w, _engine(path, dtype), path
+
+
+# ------------------------------------------------------------------------------------------ mechanisms alone
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_dynamic_tanh_kernel(dtype):
+    from stratum_b200 import kernels as K
+    rng = np.random.default_rng(0)
+    x = rng.normal(size=(37, 200)) * 3
+    w, b, alpha = rng.uniform(0.5, 1.5, 200), rng.normal(size=200) * 0.2, 0.7
+    dev = lambda a: torch.tensor(a, dtype=torch.float32, device="cuda")                     # noqa: E731
+    out = torch.empty((37, 200), dtype=torch.float32 if dtype == "float32" else torch.bfloat16, device="cuda")
+    K.dynamic_tanh(dev(x), dev([alpha]), dev(w), dev(b), out)
+    ref = N.dynamic_tanh(np.float32(x), np.float32(w), np.float32(b), np.float32(alpha))
+    assert np.max(np.abs(out.float().cpu().numpy() - ref)) <= (2e-6 if dtype == "float32" else 1e-2)
+    rows = torch.tensor([5, 0, 36], dtype=torch.int32, device="cuda")
+    part = torch.empty((3, 200), dtype=out.dtype, device="cuda")
+    K.dynamic_tanh(dev(x), dev([alpha]), dev(w), dev(b), part, rows)
+    assert torch.equal(part, out[[5, 0, 36]])
+
+
+def test_gelu_kernel_both_forms():
+    from stratum_b200 import kernels as K
+    z = np.linspace(-6, 6, 1001).astype(np.float32).reshape(7, 143)
+    for kind, ref in ((K.GELU_ERF, N.gelu_erf(z)),
+                      (K.GELU_TANH, 0.5 * z * (1 + np.tanh(np.sqrt(2 / np.pi) * (z + 0.044715 * z.astype(np.float64) ** 3))))):
+        x = torch.tensor(z, device="cuda")
+        K.gelu(x, kind)
+        assert np.max(np.abs(x.cpu().numpy() - ref)) <= 2e-6
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["latent", "diff", "ff"])
+def test_one_mechanism_alone(name, dtype, tmp_path):
+    """A model that is one mixer (or one small mixer and a feed-forward) and nothing else."""
+    from stratum_b200.engine import StepEntry
+    path, cfg, w = make(str(tmp_path / name), name, dtype, seed=5)
+    engine = _engine(path, dtype)
+    rng = np.random.default_rng(1)
+    toks = rand_tokens(rng, 90, cfg["vocab"])
+    slot = engine.acquire()
+    got = engine.step([StepEntry(slot, toks, list(range(90)))]).cpu().numpy()
+    assert_close(got, plain_logits(cfg, w, toks), dtype, name)
+
+
+def test_general_attention_kernel_window_and_cap():
+    """The kernel's parameters beyond what the architecture uses today: a window of keys, no cap, no factor."""
+    from stratum_b200 import kernels as K
+    rng = np.random.default_rng(2)
+    T, H, G, D, Dv, win = 150, 4, 2, 12, 20, 37
+    q, k, v = rng.normal(size=(T, H, D)), rng.normal(size=(T, G, D)), rng.normal(size=(T, G, Dv))
+    pages = 3
+    kc = torch.zeros((pages, G, 64, D), dtype=torch.float32, device="cuda")
+    vc = torch.zeros((pages, G, 64, Dv), dtype=torch.float32, device="cuda")
+    table = [2, 0, 1]
+    for t in range(T):
+        kc[table[t // 64], :, t % 64] = torch.tensor(k[t], dtype=torch.float32)
+        vc[table[t // 64], :, t % 64] = torch.tensor(v[t], dtype=torch.float32)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device="cuda")                       # noqa: E731
+    out = torch.empty((T, H * Dv), dtype=torch.float32, device="cuda")
+    shape = K.AttentionShape(H, H // G, 1, D, Dv, False, 0.4, window=win)
+    K.attention_general(shape, torch.tensor(q.reshape(T, -1), dtype=torch.float32, device="cuda"), kc, vc,
+                        i32(np.arange(T)), i32(np.zeros(T)), i32([table]), out, 64)
+    pos = np.arange(T)
+    ref = np.zeros((T, H, Dv))
+    for j in range(H):
+        s = q[:, j] @ k[:, j // (H // G)].T * 0.4
+        s = np.where(pos[None, :] > pos[:, None] - win, s, -np.inf)         # the last `win` keys, the token's own among them
+        ref[:, j] = N.causal_softmax(s, pos, pos) @ v[:, j // (H // G)]
+    assert np.max(np.abs(out.cpu().numpy().reshape(T, H, Dv) - ref)) <= 1e-4
+
+
+# ------------------------------------------------------------------------------------------ whole models
+def test_whole_prompt_all_positions(setup):
+    from stratum_b200.engine import StepEntry
+    name, dtype, cfg, w, engine, _ = setup
+    rng = np.random.default_rng(1)
+    for n in (1, 2, 63, 64, 65, 200):
+        toks = rand_tokens(rng, n, cfg["vocab"])
+        slot = engine.acquire()
+        got = engine.step([StepEntry(slot, toks, list(range(n)))]).cpu().numpy()
+        engine.release(slot)
+        assert_close(got, plain_logits(cfg, w, toks), dtype, f"{name} whole n={n}")
+    engine.cache.check()
+
+
+def test_prefill_against_token_by_token(setup):
+    """The same tokens whole, and one by one from the first: the same logits (float32: to rounding)."""
+    from stratum_b200.engine import StepEntry
+    name, dtype, cfg, w, engine, _ = setup
+    rng = np.random.default_rng(2)
+    n = 140
+    toks = rand_tokens(rng, n, cfg["vocab"])
+    a, b = engine.acquire(), engine.acquire()
+    whole = engine.step([StepEntry(a, toks, list(range(n)))]).cpu().numpy()
+    single = np.concatenate([engine.step([StepEntry(b, [t], [0])]).cpu().numpy() for t in toks])
+    engine.release(a); engine.release(b)
+    ref = plain_logits(cfg, w, toks)
+    assert_close(whole, ref, dtype, f"{name} whole")
+    assert_close(single, ref, dtype, f"{name} one by one")
+    if dtype == "float32":
+        assert np.max(np.abs(whole - single)) <= 2e-5 * np.max(np.abs(ref))
+
+
+@pytest.mark.parametrize("portion", [2, 3, 31, 64, 100])
+def test_prompt_in_portions(setup, portion):
+    """A prompt cut into portions of a few sizes, down to two tokens; portions start inside pages and on their
+    borders."""
+    from stratum_b200.engine import StepEntry
+    name, dtype, cfg, w, engine, _ = setup
+    rng = np.random.default_rng(portion)
+    n = 150 if portion > 3 else 70
+    toks = rand_tokens(rng, n, cfg["vocab"])
+    ref = plain_logits(cfg, w, toks)
+    slot = engine.acquire()
+    got = [engine.step([StepEntry(slot, toks[i:i + portion], list(range(len(toks[i:i + portion]))))]).cpu().numpy()
+           for i in range(0, n, portion)]
+    engine.release(slot)
+    assert_close(np.concatenate(got), ref, dtype, f"{name} portions of {portion}")
+
+
+def test_unequal_batches_against_each_alone_slots_reused(setup):
+    from stratum_b200.engine import StepEntry
+    name, dtype, cfg, w, engine, _ = setup
+    rng = np.random.default_rng(3)
+    V = cfg["vocab"]
+    for batch_no, lens in enumerate([(5, 9, 12), (1, 67), (70, 3, 33, 64)]):
+        prompts = [rand_tokens(rng, n, V) for n in lens]
+        extra = [rand_tokens(rng, k, V) for k in (3 + 2 * i for i in range(len(lens)))]
+        refs = [plain_logits(cfg, w, p + e) for p, e in zip(prompts, extra)]
+        slots = [engine.acquire() for _ in lens]
+        out = engine.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)]).cpu().numpy()
+        alone = []
+        for p in prompts:                                   # each alone, in a slot and pages of its own
+            s = engine.acquire()
+            alone.append(engine.step([StepEntry(s, p, [len(p) - 1])]).cpu().numpy()[0])
+            engine.release(s)
+        for i, p in enumerate(prompts):
+            assert_close(out[i], refs[i][len(p) - 1], dtype, f"{name} batch {batch_no} prompt {i}")
+            if dtype == "float32":
+                assert np.max(np.abs(out[i] - alone[i])) <= 2e-5 * np.max(np.abs(refs[i]))
+        live, step = list(range(len(lens))), 0
+        while live:
+            out = engine.step([StepEntry(slots[i], [extra[i][step]], [0]) for i in live]).cpu().numpy()
+            for row, i in enumerate(live):
+                assert_close(out[row], refs[i][len(prompts[i]) + step], dtype, f"{name} batch {batch_no} seq {i} +{step}")
+            step += 1
+            for i in list(live):
+                if step >= len(extra[i]):
+                    engine.release(slots[i])
+                    live.remove(i)
+        engine.cache.check()
+    assert engine.cache.tokens_held() == 0
+
+
+def test_pages_and_slots_used_again(setup):
+    """A cache of four pages: every request takes pages another one has just given back, in another order."""
+    from stratum_b200.engine import StepEntry
+    name, dtype, cfg, w, _, path = setup
+    engine = _engine(path, dtype, max_tokens=256)
+    rng = np.random.default_rng(4)
+    V = cfg["vocab"]
+    held = []
+    for n in (130, 60, 190, 64, 129):
+        while held and engine.cache.tokens_held() + ((n + 63) // 64) * 64 > 256:
+            engine.release(held.pop(0))
+        toks = rand_tokens(rng, n, V)
+        slot = engine.acquire()
+        got = engine.step([StepEntry(slot, toks[:-1], [n - 2])]).cpu().numpy()
+        got = np.concatenate([got, engine.step([StepEntry(slot, toks[-1:], [0])]).cpu().numpy()])
+        assert_close(got, plain_logits(cfg, w, toks)[-2:], dtype, f"{name} reuse n={n}")
+        held.append(slot)
+        engine.cache.check()
+
+
+def test_first_tokens_and_long_decoding(setup):
+    """Positions 0, 1, 2 one by one, then on across several pages and many steps of the query factor."""
+    from stratum_b200.engine import StepEntry
+    name, dtype, cfg, w, engine, _ = setup
+    rng = np.random.default_rng(5)
+    n = 270
+    toks = rand_tokens(rng, n, cfg["vocab"])
+    ref = plain_logits(cfg, w, toks)
+    slot = engine.acquire()
+    check = {0, 1, 2, 3} | set(range(4, n, 29)) | {63, 64, 65, 127, 128, 129, 191, 192, 193, n - 1}
+    got = []
+    for i in range(n):
+        out = engine.step([StepEntry(slot, [toks[i]], [0] if i in check else [])])
+        if i in check:
+            got.append(out.cpu().numpy())
+    engine.release(slot)
+    assert_close(np.concatenate(got), ref[sorted(check)], dtype, f"{name} long decode")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("where", [0, 1, 63, 64, 65, 128, 200])
+def test_one_far_key_decides(where, dtype, tmp_path_factory):
+    """Weights under which the last token's output is whatever one marked key, far back, carries: a lost key, a key
+    read from the wrong page or a row off by one changes the logits wholesale.  The marked token's key and the last
+    token's query are made large and parallel in both mixers (their embeddings are one large vector that the query
+    and key weights pass through); all other tokens have small embeddings."""
+    from stratum_b200.engine import StepEntry
+
+    def edit(t):
+        e = t["embed"].float()
+        e[:] = e * 0.02
+        e[7] = 0.0
+        e[7, :8] = 6.0                                   # the marked token and the asking token (id 8) share a direction
+        e[8] = 0.0
+        e[8, :8] = 6.0
+        e[8, 8:16] = 3.0                                 # ... and differ elsewhere, so that their values differ
+        t["embed"] = e.to(t["embed"].dtype)
+        for name in list(t):
+            if name.endswith((".q", ".k", ".dkv")):      # queries and keys both read the shared direction strongly
+                m = t[name].float()
+                m[:, :8] = m[:, :8].abs() * 20
+                t[name] = m.to(t[name].dtype)
+    key = f"far{where}{dtype}"
+    path, cfg, w = make(str(tmp_path_factory.mktemp(key)), "TC", dtype, seed=9, edit=edit)
+    engine = _engine(path, dtype)
+    rng = np.random.default_rng(where)
+    n = 260
+    toks = [int(t) for t in rng.integers(9, cfg["vocab"], n)]
+    toks[where], toks[-1] = 7, 8
+    ref = plain_logits(cfg, w, toks)
+    moved = list(toks)
+    moved[where] = toks[where + 1] if where + 1 < n - 1 else 9
+    assert np.max(np.abs(plain_logits(cfg, w, moved)[-1] - ref[-1])) > 0.05 * np.max(np.abs(ref[-1])), "the key does not matter"
+    slot = engine.acquire()
+    whole = engine.step([StepEntry(slot, toks, [n - 1])]).cpu().numpy()[0]
+    engine.release(slot)
+    slot = engine.acquire()
+    engine.step([StepEntry(slot, toks[:n - 1], [])])
+    decoded = engine.step([StepEntry(slot, toks[n - 1:], [0])]).cpu().numpy()[0]
+    engine.release(slot)
+    assert_close(whole, ref[-1], dtype, f"far key at {where}, whole")
+    assert_close(decoded, ref[-1], dtype, f"far key at {where}, decoded")
+
+
+# ------------------------------------------------------------------------------------------ generation
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_greedy_generation_through_the_entry_point(dtype, tmp_path):
+    """Stratum.generate: the scheduler's batches, replayed decode graphs, slots given back; every picked token is the
+    plain implementation's best (or within rounding of it)."""
+    from stratum_b200 import Stratum
+    path, cfg, w = make(str(tmp_path / "gen"), "A", dtype, seed=11)
+    rng = np.random.default_rng(0)
+    prompts = [rand_tokens(rng, n, cfg["vocab"]) for n in (5, 70, 12, 1)]
+    llm = Stratum(path, dtype=dtype, max_tokens=1024)
+    res = llm.generate(prompts, max_new_tokens=10, stop_ids=())
+    for p, r in zip(prompts, res):
+        assert len(r.tokens) == 10
+        seq = list(p)
+        for tok in r.tokens:
+            ref = plain_logits(cfg, w, seq)[-1]
+            assert ref[tok] >= ref.max() - 2 * TOL[dtype] * float(np.max(np.abs(ref))), (p, r.tokens, tok)
+            seq.append(tok)
+    serial = llm.generate(prompts, max_new_tokens=10, stop_ids=(), max_batch=2)
+    if dtype == "float32":
+        assert [r.tokens for r in serial] == [r.tokens for r in res]
+    llm.engine.cache.check()
+    assert llm.engine.cache.tokens_held() == 0
