@@ -26,9 +26,11 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC",
                            "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
 SOURCES = ("elementwise", "linear_simple", "attention_simple", "sampling", "gemm_skinny", "attention_mma",
-           "gemm_tc", "attention_tc", "attention_stream", "attention_static", "attention_general", "mixer_prep")
+           "gemm_tc", "attention_tc", "attention_stream", "attention_static", "attention_general", "attention_general_mma",
+           "mixer_prep")
 HEADERS = ("common.cuh",)
 EXTRA_DEPS = {"attention_general": ("attention_general.h",),
+              "attention_general_mma": ("attention_general.h", "mma_common.cuh"),
               "attention_static": ("attention_mma.cu", "attention_static.h", "mma_common.cuh"),   # files a source includes
               "attention_mma": ("mma_common.cuh",), "attention_stream": ("mma_common.cuh", "tc_common.cuh"),
               "gemm_tc": ("tc_common.cuh",), "attention_tc": ("tc_common.cuh",)}

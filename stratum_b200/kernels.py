@@ -621,6 +621,43 @@ def attention_general(shape: AttentionShape, q: torch.Tensor, k_cache: torch.Ten
     _check(f(ctypes.addressof(p), dtype_code(q.dtype), _stream()), "attention_general")
 
 
+def attention_general_mma_ok(shape: AttentionShape, q: torch.Tensor, out: torch.Tensor, page_tokens: int) -> bool:
+    """Whether the tensor-core form of the general attention takes this call (else: attention_general)."""
+    return (q.dtype == torch.bfloat16 and shape.qk_dim % 8 == 0 and shape.v_dim % 8 == 0 and shape.v_dim <= 512
+            and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
+            and out.data_ptr() % 16 == 0 and page_tokens == 64)
+
+
+def attention_general_mma(shape: AttentionShape, q: torch.Tensor, k_cache: torch.Tensor,
+                          v_cache: Optional[torch.Tensor], token_pos: torch.Tensor, token_seq: torch.Tensor,
+                          block_table: torch.Tensor, out: torch.Tensor, page_tokens: int, qblocks,
+                          tokens_per_block: int, n_splits: int, chunk: int, part_o: Optional[torch.Tensor],
+                          part_ml: Optional[torch.Tensor]) -> None:
+    """The general attention in bfloat16 on tensor cores.  qblocks: None (one token per sequence, block i is row i)
+    or (seq, first row, tokens) int32 tensors with tokens <= tokens_per_block = 16 // min(group, 16).  The keys
+    of a sequence are cut into n_splits ranges of `chunk` keys (a multiple of 64).  With more than one range or
+    more than one map the items' results go through scratch: part_o float32 [tokens*heads*maps*n_splits*v_dim],
+    part_ml float32 [tokens*heads*maps*n_splits*2]."""
+    p = _general_params(shape, q, k_cache, v_cache, token_pos, token_seq, block_table, out, page_tokens)
+    if qblocks is None:
+        p.n_qblocks = q.shape[0]
+    else:
+        qs, qt, qn = qblocks
+        p.qb_seq, p.qb_tok0, p.qb_ntok, p.n_qblocks = qs.data_ptr(), qt.data_ptr(), qn.data_ptr(), qs.numel()
+    p.tokens_per_block, p.n_splits, p.chunk = tokens_per_block, n_splits, chunk
+    through_scratch = n_splits > 1 or shape.maps > 1
+    if through_scratch:
+        need = q.shape[0] * shape.n_heads * shape.maps * n_splits
+        _need(part_o, "part_o", torch.float32); _need(part_ml, "part_ml", torch.float32)
+        if part_o.numel() < need * shape.v_dim or part_ml.numel() < need * 2:
+            raise KernelError("attention_general_mma: scratch too small")
+        p.part_o, p.part_ml = part_o.data_ptr(), part_ml.data_ptr()
+    f = _fn("attention_general_mma", "stratum_attention_general_mma", [c_void_p, c_void_p])
+    _check(f(ctypes.addressof(p), _stream()), "attention_general_mma")
+    if through_scratch:
+        count_launches(1)          # the finishing kernel
+
+
 def attention_mma(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, token_pos: torch.Tensor,
                   token_seq: torch.Tensor, block_table: torch.Tensor, qblocks, tokens_per_block: int,
                   out: torch.Tensor, part_o: Optional[torch.Tensor], part_ml: Optional[torch.Tensor], n_q: int,

@@ -82,8 +82,43 @@ def run(att, qkv: torch.Tensor, cache, step, out: torch.Tensor) -> None:
                          PAGE_TOKENS, att.window, att.scale)
 
 
+# CTAs wanted in flight on decode steps of the general attention: 148 SMs times the CTAs of four warps an SM holds
+GENERAL_TARGET_CTAS = int(os.environ.get("STRATUM_GENERAL_ATTENTION_CTAS", 148 * 4))
+GENERAL_MAX_SPLITS = 64
+
+
+def plan_general_splits(n_items: int, max_len: int):
+    """(n_splits, keys per split) for decode steps of the general attention: whole pages per split."""
+    pages = max(1, (max_len + PAGE_TOKENS - 1) // PAGE_TOKENS)
+    want = max(1, min(pages, GENERAL_MAX_SPLITS, (GENERAL_TARGET_CTAS + n_items - 1) // n_items))
+    chunk = ((pages + want - 1) // want) * PAGE_TOKENS
+    return (max_len + chunk - 1) // chunk, chunk
+
+
 def run_general(att, shape, q: torch.Tensor, cache, step, out: torch.Tensor) -> None:
     """Attention of the shapes kernels.AttentionShape describes (key and value sizes of their own, values inside the
-    key rows, several maps per head): q [tokens, *] holds head j's map m at column (j * maps + m) * qk_dim."""
-    K.attention_general(shape, q, cache.k, cache.v, step.token_pos, step.token_seq, cache.block_table, out,
-                        PAGE_TOKENS)
+    key rows, several maps per head): q [tokens, *] holds head j's map m at column (j * maps + m) * qk_dim.
+    bfloat16 with sizes in multiples of 8: the tensor-core kernel (decode steps: the keys cut into ranges that
+    fill the GPU; prompts: query blocks of 16 rows); everything else: the CUDA-core kernel, float32 throughout.
+    STRATUM_GENERAL_ATTENTION_MMA=0: always the CUDA-core kernel (measurements)."""
+    if (not K.attention_general_mma_ok(shape, q, out, PAGE_TOKENS)
+            or os.environ.get("STRATUM_GENERAL_ATTENTION_MMA", "1") == "0"):
+        K.attention_general(shape, q, cache.k, cache.v, step.token_pos, step.token_seq, cache.block_table, out,
+                            PAGE_TOKENS)
+        return
+    rows_per_token = min(shape.group, 16)
+    per_block = 16 // rows_per_token
+    streams = (shape.n_heads // shape.group) * ((shape.group + 15) // 16) * shape.maps
+    if step.all_single:
+        qblocks = None
+        n_splits, chunk = plan_general_splits(step.n_tokens * streams, step.max_len)
+    else:
+        qblocks = step.query_blocks(per_block)
+        n_splits, chunk = 1, ((step.max_len + PAGE_TOKENS - 1) // PAGE_TOKENS) * PAGE_TOKENS
+    part_o = part_ml = None
+    if n_splits > 1 or shape.maps > 1:
+        n = step.n_tokens * shape.n_heads * shape.maps * n_splits
+        part_o = att.runtime.scratch("general_attention_part_o", n * shape.v_dim, torch.float32)
+        part_ml = att.runtime.scratch("general_attention_part_ml", n * 2, torch.float32)
+    K.attention_general_mma(shape, q, cache.k, cache.v, step.token_pos, step.token_seq, cache.block_table, out,
+                            PAGE_TOKENS, qblocks, per_block, n_splits, chunk, part_o, part_ml)

@@ -285,3 +285,82 @@ def test_greedy_generation_through_the_entry_point(dtype, tmp_path):
         assert [r.tokens for r in serial] == [r.tokens for r in res]
     llm.engine.cache.check()
     assert llm.engine.cache.tokens_held() == 0
+
+
+# ------------------------------------------------------------------------------------------ tensor-core attention
+def _fill_cache(rng, seq_lens, n_k, D, n_v, Dv, v_in_k):
+    """A paged cache with shuffled pages holding random keys (and values) for sequences of the given lengths."""
+    pages_of = [(n + 63) // 64 for n in seq_lens]
+    order = rng.permutation(sum(pages_of) + 3)
+    tables, at = [], 0
+    for n in pages_of:
+        tables.append([int(x) for x in order[at:at + n]])
+        at += n
+    width = max(pages_of)
+    kc = torch.zeros((len(order), n_k, 64, D), dtype=torch.bfloat16, device="cuda")
+    vc = None if v_in_k else torch.zeros((len(order), n_v, 64, Dv), dtype=torch.bfloat16, device="cuda")
+    for tb, n in zip(tables, seq_lens):
+        for j, page in enumerate(tb):
+            m = min(64, n - 64 * j)
+            kc[page, :, :m] = torch.tensor(rng.normal(size=(n_k, m, D)), dtype=torch.bfloat16)
+            if vc is not None:
+                vc[page, :, :m] = torch.tensor(rng.normal(size=(n_v, m, Dv)), dtype=torch.bfloat16)
+    table = torch.tensor([tb + [-1] * (width - len(tb)) for tb in tables], dtype=torch.int32, device="cuda")
+    return kc, vc, table
+
+
+@pytest.mark.parametrize("case", [
+    # heads, group, maps, D, Dv, v_in_k, new tokens per sequence, cached before
+    dict(H=4, group=4, maps=1, D=144, Dv=128, v_in_k=True, new=(1, 1, 1), before=(0, 63, 700)),
+    dict(H=16, group=16, maps=1, D=576, Dv=512, v_in_k=True, new=(1, 1), before=(300, 1100)),
+    dict(H=20, group=20, maps=1, D=72, Dv=64, v_in_k=True, new=(5, 70), before=(0, 130)),
+    dict(H=4, group=4, maps=2, D=48, Dv=96, v_in_k=False, new=(1, 1, 1, 1), before=(5, 64, 127, 900)),
+    dict(H=6, group=2, maps=2, D=16, Dv=24, v_in_k=False, new=(33, 1, 130), before=(0, 77, 64)),
+    dict(H=8, group=8, maps=1, D=40, Dv=40, v_in_k=True, new=(150,), before=(0,), window=37),
+])
+def test_tensor_core_attention_against_cuda_cores(case):
+    """The same bfloat16 queries and cache through both kernels: decode steps with the keys cut into ranges,
+    prompts in query blocks, sizes up to those of a large model's latent, two maps combined, a window."""
+    from stratum_b200 import kernels as K
+    rng = np.random.default_rng(7)
+    H, group, maps, D, Dv, v_in_k = (case[k] for k in ("H", "group", "maps", "D", "Dv", "v_in_k"))
+    new, before = case["new"], case["before"]
+    lens = [a + b for a, b in zip(new, before)]
+    n_k, n_v = (H // group) * maps, H // group
+    kc, vc, table = _fill_cache(rng, lens, n_k, D, n_v, Dv, v_in_k)
+    T = sum(new)
+    pos = np.concatenate([np.arange(b, b + n) for n, b in zip(new, before)])
+    seq = np.concatenate([np.full(n, i) for i, n in enumerate(new)])
+    gate = maps == 2
+    width = H * maps * D + (H if gate else 0)
+    ld = (width + 7) // 8 * 8
+    q = torch.zeros((T, ld), dtype=torch.bfloat16, device="cuda")
+    q[:, :width] = torch.tensor(rng.normal(size=(T, width)) * 0.5, dtype=torch.bfloat16)
+    i32 = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device="cuda")          # noqa: E731
+    shape = K.AttentionShape(H, group, maps, D, Dv, v_in_k, 0.3, softcap=5.0 if gate else 0.0,
+                             window=case.get("window", 0), temp_coef=0.4 if gate else 0.0, temp_every=50,
+                             lam=0.45, out_scale=0.7, eps=1e-5, gate_col=H * maps * D if gate else -1)
+    ref = torch.zeros((T, (H * Dv + 7) // 8 * 8), dtype=torch.bfloat16, device="cuda")
+    K.attention_general(shape, q, kc, vc, i32(pos), i32(seq), table, ref, 64)
+    per_block = 16 // min(group, 16)
+    single = all(n == 1 for n in new)
+    for n_splits, chunk in ([(1, 2048), (3, 384), (16, 128)] if single else [(1, 2048)]):
+        qblocks = None
+        if not single:
+            qs, qt, qn, r = [], [], [], 0
+            for i, n in enumerate(new):
+                for b in range(0, n, per_block):
+                    qs.append(i); qt.append(r + b); qn.append(min(per_block, n - b))
+                r += n
+            qblocks = (i32(qs), i32(qt), i32(qn))
+        n_part = T * H * maps * n_splits
+        part_o = torch.full((n_part * Dv,), float("nan"), dtype=torch.float32, device="cuda")
+        part_ml = torch.full((n_part * 2,), float("nan"), dtype=torch.float32, device="cuda")
+        out = torch.zeros_like(ref)
+        K.attention_general_mma(shape, q, kc, vc, i32(pos), i32(seq), table, out, 64, qblocks, per_block, n_splits,
+                                chunk, part_o, part_ml)
+        torch.cuda.synchronize()
+        a, b = out.float().cpu().numpy()[:, :H * Dv], ref.float().cpu().numpy()[:, :H * Dv]
+        assert np.isfinite(a).all()
+        # both round their result to bfloat16 once: one unit in the last place of the larger values
+        assert np.max(np.abs(a - b)) <= 2 ** -7 * max(1.0, np.max(np.abs(b))), (n_splits, np.max(np.abs(a - b)))
