@@ -3,6 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers L]
     python bench.py --impl reference        # the reference arm (see below)
+    python bench.py --compare nibelorn      # the Nibelorn decoder beside a Llama decoder of equal size (one JSON line)
 
 Prints ONE JSON line.  `value` is decoded tokens per second at the given batch, with every
 sequence's cache filled to the given context at the end of the timed steps (so the timed steps
@@ -53,6 +54,78 @@ OTHER_SHAPES = {
                         rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
                                       "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}),
 }
+# --compare nibelorn: layer sizes that resemble a 1B and an 8B model's, for the Nibelorn decoder and for a Llama
+# decoder of equal width, heads, layers and vocabulary whose SwiGLU holds as many weights as the dense feed-forward
+# (3 x width x inner = 2 x width x ff).  Three latent-attention layers to one differential-attention layer.
+COMPARE_SIZES = {
+    "1b": {"width": 2048, "vocab": 32768, "ff": 8192, "heads": 16, "kv_heads": 4, "llama_head_dim": 128,
+           "llama_inner": 5504, "latent": {"dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 256},
+           "diff": {"dim": 64, "vdim": 128}},
+    "8b": {"width": 4096, "vocab": 32768, "ff": 16384, "heads": 32, "kv_heads": 8, "llama_head_dim": 128,
+           "llama_inner": 10880, "latent": {"dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512},
+           "diff": {"dim": 64, "vdim": 128}},
+}
+
+
+def nibelorn_config(size, n_layers):
+    from stratum_b200.config import NibelornConfig
+    z = COMPARE_SIZES[size]
+    lat, dif = z["latent"], z["diff"]
+    latent = {"heads": z["heads"], "dim": lat["dim"], "rot_dim": lat["rot_dim"], "vdim": lat["vdim"],
+              "kv_rank": lat["kv_rank"], "scale": (lat["dim"] + lat["rot_dim"]) ** -0.5,
+              "rot": {"base": 10000.0, "dims": lat["rot_dim"]}}
+    diff = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": dif["dim"], "vdim": dif["vdim"],
+            "scale": dif["dim"] ** -0.5, "softcap": 30.0, "diff": 0.2, "q_temp": {"coef": 0.1, "every": 1024}}
+    layers = [{"type": "attention", "mixer": diff, "mlp": {"kind": "dense", "ff": z["ff"]}} if i % 4 == 2 else
+              {"type": "latent_attention", "mixer": latent, "mlp": {"kind": "dense", "ff": z["ff"]}}
+              for i in range(n_layers)]
+    return NibelornConfig.from_dict({"architecture": "Nibelorn", "vocab": z["vocab"], "width": z["width"],
+                                     "norm": {"eps": 1e-6}, "layers": layers})
+
+
+def llama_like(size, n_layers):
+    from stratum_b200.config import LlamaConfig
+    z = COMPARE_SIZES[size]
+    return LlamaConfig.from_dict({
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": n_layers,
+        "hidden_size": z["width"], "intermediate_size": z["llama_inner"], "num_attention_heads": z["heads"],
+        "num_key_value_heads": z["kv_heads"], "head_dim": z["llama_head_dim"], "vocab_size": z["vocab"],
+        "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 8192,
+        "tie_word_embeddings": False, "hidden_act": "silu", "torch_dtype": "bfloat16"})
+
+
+def compare_nibelorn(args, rng):
+    """Prefill and decode throughput of the Nibelorn decoder beside a Llama decoder of equal size: one prompt of
+    --prefill-tokens, and decode steps of --batch sequences at --context tokens (random bf16 weights, device-timed
+    as the main workload is).  One JSON line."""
+    import torch
+    from stratum_b200 import Stratum
+    n_layers = args.layers or 8
+    out = {"compare": "nibelorn", "layers": n_layers, "batch": args.batch, "context": args.context,
+           "prefill_tokens": args.prefill_tokens, "dtype": "bf16", "data": "synthetic: random-init weights",
+           "sizes": {}}
+    for size in sorted(COMPARE_SIZES):
+        row = {}
+        for name, cfg in (("nibelorn", nibelorn_config(size, n_layers)), ("llama", llama_like(size, n_layers))):
+            llm = Stratum.from_random(cfg, seed=0, dtype="bfloat16",
+                                      max_tokens=max(args.batch * (args.context + 64), args.prefill_tokens + 64),
+                                      max_seqs=args.batch)
+            ms_step, launches = time_decode(llm, args.batch, args.context, args.steps, max(args.warmup, 3), cfg.vocab,
+                                            rng)
+            pf_ms = time_prefill(llm, args.prefill_tokens, cfg.vocab, rng, repeats=2)
+            row[name] = {"decode_tok_per_s": round(args.batch * 1000.0 / ms_step, 1),
+                         "decode_ms_per_step": round(ms_step, 4), "launches_per_step": launches,
+                         "prefill_tok_per_s": round(args.prefill_tokens * 1000.0 / pf_ms, 1),
+                         "prefill_ms": round(pf_ms, 3)}
+            del llm
+            torch.cuda.empty_cache()
+        row["decode_ratio"] = round(row["nibelorn"]["decode_tok_per_s"] / row["llama"]["decode_tok_per_s"], 3)
+        row["prefill_ratio"] = round(row["nibelorn"]["prefill_tok_per_s"] / row["llama"]["prefill_tok_per_s"], 3)
+        out["sizes"][size] = row
+    print(json.dumps(out))
+    return 0
+
+
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 PREFILL_TOKENS = 2048
 
@@ -280,6 +353,9 @@ def main() -> int:
                     help="prompt length of --prefill-only (the JSON line of the contract always uses 2,048)")
     ap.add_argument("--shape", default="llama3.1-8b", choices=["llama3.1-8b"] + sorted(OTHER_SHAPES),
                     help="layer sizes for the short lines of --decode-only / --prefill-only")
+    ap.add_argument("--compare", default=None, choices=["nibelorn"],
+                    help="instead of the main workload: prefill and decode throughput of the Nibelorn decoder beside a "
+                         "Llama decoder of equal size, at 1B-like and 8B-like layer sizes (--layers of them, default 8)")
     ap.add_argument("--prefill-only", action="store_true",
                     help="time the 2,048-token prompt only and print a short line (for profiler runs)")
     args = ap.parse_args()
@@ -300,6 +376,8 @@ def main() -> int:
     from stratum_b200 import Stratum, kernels
     from stratum_b200.config import LlamaConfig
 
+    if args.compare:
+        return compare_nibelorn(args, np.random.default_rng(0))
     raw = dict(LLAMA_31_8B if args.shape == "llama3.1-8b" else OTHER_SHAPES[args.shape])
     if raw.get("rope_scaling") is None:
         raw.pop("rope_scaling", None)

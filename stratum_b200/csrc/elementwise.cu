@@ -215,8 +215,7 @@ STRATUM_EXPORT int stratum_dynamic_tanh(const float* x, const float* alpha, cons
 // In place over [rows][ld], the first `width` columns of every row.
 // kind 0: z * 0.5 * (1 + erf(z / sqrt 2));  kind 1: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
 __device__ __forceinline__ float gelu_value(float z, int kind) {
-  if (kind == 0) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
-  return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+  return activate(z, kind == 0 ? STRATUM_ACT_GELU_ERF : STRATUM_ACT_GELU_TANH);
 }
 
 template <typename T>

@@ -46,7 +46,7 @@ __device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], uint32_t a0, uin
 template <int MT, int RT, int EPI>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const float* __restrict__ bias,
-                   void* __restrict__ out, int M, int N, int K, int ldx, int ldo, int groups_per_block) {
+                   void* __restrict__ out, int M, int N, int K, int ldx, int ldo, int groups_per_block, int act) {
   constexpr int KS = SK_WARPS / RT;                 // K parts
   __shared__ float part[RT][KS][MT * 8][16 + 1];    // [row tile][k part][x row][weight row]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -145,7 +145,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
       for (int s = 0; s < KS; s++) v += part[tile][s][m][r];
       if (bias) v += bias[n];
       const size_t o = (size_t)m * ldo + n;
-      if (EPI == 0) ((bf16*)out)[o] = __float2bfloat16_rn(v);
+      if (EPI == 0) ((bf16*)out)[o] = __float2bfloat16_rn(activate(v, act));
       else if (EPI == 1) ((float*)out)[o] = ld_fresh((const float*)out + o) + v;
       else ((float*)out)[o] = v;
     }
@@ -182,7 +182,7 @@ static int sm_count() {
 
 template <int MT, int RT, int EPI>
 static int launch_skinny_epi(const bf16* x, const bf16* w, const float* bias, void* out, int M, int N, int K,
-                             int ldx, int ldo, cudaStream_t stream) {
+                             int ldx, int ldo, int act, cudaStream_t stream) {
   auto kern = gemm_skinny_kernel<MT, RT, EPI>;
   static int resident = 0;                 // blocks of this kernel the whole GPU holds at once
   if (!resident) {
@@ -194,26 +194,28 @@ static int launch_skinny_epi(const bf16* x, const bf16* w, const float* bias, vo
   const int n_groups = (N + 16 * RT - 1) / (16 * RT);
   const int per_block = (n_groups + resident - 1) / resident;
   const int blocks = (n_groups + per_block - 1) / per_block;
-  return launch_pdl(kern, blocks, SK_WARPS * 32, 0, stream, x, w, bias, out, M, N, K, ldx, ldo, per_block);
+  return launch_pdl(kern, blocks, SK_WARPS * 32, 0, stream, x, w, bias, out, M, N, K, ldx, ldo, per_block, act);
 }
 
 template <int MT, int RT>
 static int launch_skinny(const bf16* x, const bf16* w, const float* bias, void* out, int epilogue, int M, int N,
-                         int K, int ldx, int ldo, cudaStream_t stream) {
+                         int K, int ldx, int ldo, int act, cudaStream_t stream) {
   switch (epilogue) {
-    case 0: return launch_skinny_epi<MT, RT, 0>(x, w, bias, out, M, N, K, ldx, ldo, stream);
-    case 1: return launch_skinny_epi<MT, RT, 1>(x, w, bias, out, M, N, K, ldx, ldo, stream);
-    case 2: return launch_skinny_epi<MT, RT, 2>(x, w, bias, out, M, N, K, ldx, ldo, stream);
-    case 3: return launch_skinny_epi<MT, RT, 3>(x, w, bias, out, M, N, K, ldx, ldo, stream);
+    case 0: return launch_skinny_epi<MT, RT, 0>(x, w, bias, out, M, N, K, ldx, ldo, act, stream);
+    case 1: return launch_skinny_epi<MT, RT, 1>(x, w, bias, out, M, N, K, ldx, ldo, act, stream);
+    case 2: return launch_skinny_epi<MT, RT, 2>(x, w, bias, out, M, N, K, ldx, ldo, act, stream);
+    case 3: return launch_skinny_epi<MT, RT, 3>(x, w, bias, out, M, N, K, ldx, ldo, act, stream);
     default: return STRATUM_ERR_SHAPE;
   }
 }
 
 // x: bf16 [M][ldx], w: bf16 [N][K], bias float32 [N] or null, out [M][ldo] (for SwiGLU: [M][N/2]).
 // Needs K % 8 == 0, ldx % 8 == 0 and 16-byte aligned x and w (checked); M <= 32.
-STRATUM_EXPORT int stratum_gemm_skinny(const void* x, const void* w, const float* bias, void* out, int epilogue,
-                                       int M, int N, int K, int ldx, int ldo, cudaStream_t stream) {
+// act (epilogue 0 only): an activation applied to what is stored, see common.cuh.
+STRATUM_EXPORT int stratum_gemm_skinny_act(const void* x, const void* w, const float* bias, void* out, int epilogue,
+                                           int M, int N, int K, int ldx, int ldo, int act, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
+  if (act != 0 && epilogue != 0) return STRATUM_ERR_SHAPE;
   if (M > 32) return STRATUM_ERR_LIMIT;
   if (K <= 0 || K % 8 != 0 || ldx % 8 != 0) return STRATUM_ERR_SHAPE;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return STRATUM_ERR_ALIGN;
@@ -222,10 +224,15 @@ STRATUM_EXPORT int stratum_gemm_skinny(const void* x, const void* w, const float
   const bf16* wb = (const bf16*)w;
   // few weight rows: one 16-row tile per block (more blocks, K cut 8 ways); many: two tiles, K cut 4 ways
   const bool small_n = N < 16 * 2 * 148 * 2;
-  if (M <= 8) return small_n ? launch_skinny<1, 1>(xb, wb, bias, out, epilogue, M, N, K, ldx, ldo, stream)
-                             : launch_skinny<1, 2>(xb, wb, bias, out, epilogue, M, N, K, ldx, ldo, stream);
-  if (M <= 16) return small_n ? launch_skinny<2, 1>(xb, wb, bias, out, epilogue, M, N, K, ldx, ldo, stream)
-                              : launch_skinny<2, 2>(xb, wb, bias, out, epilogue, M, N, K, ldx, ldo, stream);
-  return small_n ? launch_skinny<4, 1>(xb, wb, bias, out, epilogue, M, N, K, ldx, ldo, stream)
-                 : launch_skinny<4, 2>(xb, wb, bias, out, epilogue, M, N, K, ldx, ldo, stream);
+  if (M <= 8) return small_n ? launch_skinny<1, 1>(xb, wb, bias, out, epilogue, M, N, K, ldx, ldo, act, stream)
+                             : launch_skinny<1, 2>(xb, wb, bias, out, epilogue, M, N, K, ldx, ldo, act, stream);
+  if (M <= 16) return small_n ? launch_skinny<2, 1>(xb, wb, bias, out, epilogue, M, N, K, ldx, ldo, act, stream)
+                              : launch_skinny<2, 2>(xb, wb, bias, out, epilogue, M, N, K, ldx, ldo, act, stream);
+  return small_n ? launch_skinny<4, 1>(xb, wb, bias, out, epilogue, M, N, K, ldx, ldo, act, stream)
+                 : launch_skinny<4, 2>(xb, wb, bias, out, epilogue, M, N, K, ldx, ldo, act, stream);
+}
+
+STRATUM_EXPORT int stratum_gemm_skinny(const void* x, const void* w, const float* bias, void* out, int epilogue,
+                                       int M, int N, int K, int ldx, int ldo, cudaStream_t stream) {
+  return stratum_gemm_skinny_act(x, w, bias, out, epilogue, M, N, K, ldx, ldo, 0, stream);
 }

@@ -55,7 +55,7 @@ struct EpiExtra {
   int norm_parts, norm_ld; float norm_size, norm_eps;
   int emit_ldx, emit_ld;
   int rope_pairs, bt_stride, n_q, n_kv, head_dim, page_tokens, write_cache;
-  int reserved;
+  int act;            // epilogue 0: an activation applied to what is stored (common.cuh)
 };
 
 __device__ __forceinline__ float epi_row_scale(const EpiExtra& X, int m) {
@@ -201,6 +201,10 @@ __device__ __forceinline__ void tc_store_chunk(const TcParams& P, int m, int col
     }
   } else if (EPI == 0) {
     bf16* o = (bf16*)P.out + (size_t)m * P.ldo + col0;
+    if (P.X.act) {
+#pragma unroll
+      for (int j = 0; j < CW; j++) v[j] = activate(v[j], P.X.act);
+    }
     if (whole && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
 #pragma unroll
       for (int q = 0; q < CW / 8; q++) {
@@ -289,6 +293,10 @@ __device__ __forceinline__ void fixup_store(const PT& P, int m, int n, float4 v)
   const bool wide = (n + 3 < P.N) && ((idx & 3) == 0);
   if (EPI == 0) {
     bf16* o = (bf16*)P.out + idx;
+    if (P.X.act) {
+#pragma unroll
+      for (int j = 0; j < 4; j++) e[j] = activate(e[j], P.X.act);
+    }
     if (wide && ((reinterpret_cast<uintptr_t>(o) & 7) == 0)) {
       __nv_bfloat162 lo = __floats2bfloat162_rn(e[0], e[1]), hi = __floats2bfloat162_rn(e[2], e[3]);
       uint2 u; u.x = *reinterpret_cast<uint32_t*>(&lo); u.y = *reinterpret_cast<uint32_t*>(&hi);
@@ -822,7 +830,7 @@ __device__ __forceinline__ void sk_store(const SkParams& P, const SkTables& T, i
         ((bf16*)P.out)[(size_t)m * P.ldo + (n >> 1)] = __float2bfloat16_rn(val / (1.0f + __expf(-val)) * other);
     } else if (m < P.M && n < P.N) {
       const size_t idx = (size_t)m * P.ldo + n;
-      if (EPI == 0) ((bf16*)P.out)[idx] = __float2bfloat16_rn(val);
+      if (EPI == 0) ((bf16*)P.out)[idx] = __float2bfloat16_rn(activate(val, P.X.act));
       else ((float*)P.out)[idx] = val;
     }
   }

@@ -21,7 +21,7 @@ template <typename T, int EPI>
 __global__ void __launch_bounds__(256)
 linear_simple_kernel(const T* __restrict__ x, const T* __restrict__ w, const float* __restrict__ bias,
                      void* __restrict__ out, int M, int N, int K, int ldx, int ldo, int x_step, long long w_step,
-                     int o_step) {
+                     int o_step, int act) {
   __shared__ float xs[LS_BK][LS_BM + 1];
   __shared__ float ws[LS_BK][LS_BN + 1];
   const int tid = threadIdx.x;
@@ -73,7 +73,7 @@ linear_simple_kernel(const T* __restrict__ x, const T* __restrict__ w, const flo
       float v = acc[i][j];
       if (bias) v += bias[n];
       const size_t o = (size_t)m * ldo + n + o_shift;
-      if (EPI == 0) ((T*)out)[o] = from_float<T>(v);
+      if (EPI == 0) ((T*)out)[o] = from_float<T>(activate(v, act));
       else if (EPI == 1) ((float*)out)[o] += v;
       else ((float*)out)[o] = v;
     }
@@ -83,32 +83,42 @@ linear_simple_kernel(const T* __restrict__ x, const T* __restrict__ w, const flo
 template <typename T>
 static int launch_linear_simple(const void* x, const void* w, const float* bias, void* out, int epilogue,
                                 int M, int N, int K, int ldx, int ldo, cudaStream_t stream, int heads = 1,
-                                int x_step = 0, long long w_step = 0, int o_step = 0) {
+                                int x_step = 0, long long w_step = 0, int o_step = 0, int act = 0) {
   dim3 grid((N + LS_BN - 1) / LS_BN, (M + LS_BM - 1) / LS_BM, heads);
   if (epilogue == 0)
     linear_simple_kernel<T, 0><<<grid, 256, 0, stream>>>((const T*)x, (const T*)w, bias, out, M, N, K, ldx, ldo,
-                                                      x_step, w_step, o_step);
+                                                      x_step, w_step, o_step, act);
   else if (epilogue == 1)
     linear_simple_kernel<T, 1><<<grid, 256, 0, stream>>>((const T*)x, (const T*)w, bias, out, M, N, K, ldx, ldo,
-                                                      x_step, w_step, o_step);
+                                                      x_step, w_step, o_step, act);
   else if (epilogue == 2)
     linear_simple_kernel<T, 2><<<grid, 256, 0, stream>>>((const T*)x, (const T*)w, bias, out, M, N, K, ldx, ldo,
-                                                      x_step, w_step, o_step);
+                                                      x_step, w_step, o_step, act);
   else
     return STRATUM_ERR_SHAPE;
   return launch_status();
 }
 
 // x: [M][ldx] T (first K columns used); w: [N][K] T; bias: float32 [N] or null; out: [M][ldo].
+// act (epilogue 0 only): an activation applied to what is stored, see common.cuh.
+STRATUM_EXPORT int stratum_linear_simple_act(const void* x, const void* w, const float* bias, void* out, int dtype,
+                                             int epilogue, int M, int N, int K, int ldx, int ldo, int act,
+                                             cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || ldx < K || ldo < N) return STRATUM_ERR_SHAPE;
+  if (act != 0 && epilogue != 0) return STRATUM_ERR_SHAPE;
+  if ((M + LS_BM - 1) / LS_BM > 65535) return STRATUM_ERR_LIMIT;
+  if (dtype == STRATUM_DT_F32)
+    return launch_linear_simple<float>(x, w, bias, out, epilogue, M, N, K, ldx, ldo, stream, 1, 0, 0, 0, act);
+  if (dtype == STRATUM_DT_BF16)
+    return launch_linear_simple<bf16>(x, w, bias, out, epilogue, M, N, K, ldx, ldo, stream, 1, 0, 0, 0, act);
+  return STRATUM_ERR_DTYPE;
+}
+
 STRATUM_EXPORT int stratum_linear_simple(const void* x, const void* w, const float* bias, void* out, int dtype,
                                          int epilogue, int M, int N, int K, int ldx, int ldo,
                                          cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || ldx < K || ldo < N) return STRATUM_ERR_SHAPE;
-  if ((M + LS_BM - 1) / LS_BM > 65535) return STRATUM_ERR_LIMIT;
-  if (dtype == STRATUM_DT_F32) return launch_linear_simple<float>(x, w, bias, out, epilogue, M, N, K, ldx, ldo, stream);
-  if (dtype == STRATUM_DT_BF16) return launch_linear_simple<bf16>(x, w, bias, out, epilogue, M, N, K, ldx, ldo, stream);
-  return STRATUM_ERR_DTYPE;
+  return stratum_linear_simple_act(x, w, bias, out, dtype, epilogue, M, N, K, ldx, ldo, 0, stream);
 }
 
 // The same product once per head: head j multiplies columns [j * x_step, j * x_step + K) of x by the matrix

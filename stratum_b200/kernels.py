@@ -271,9 +271,13 @@ EPI_STORE, EPI_ADD_F32, EPI_STORE_F32, EPI_SWIGLU = 0, 1, 2, 3
 EPI_ADD_F32_EMIT, EPI_QKV_ROPE = 4, 5          # gemm_tc only: see GemmExtra
 
 
+ACT_NONE, ACT_GELU_ERF, ACT_GELU_TANH = 0, 1, 2       # what a product with EPI_STORE may apply to what it stores
+
+
 def linear_simple(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-                  epilogue: int) -> None:
-    """out (=|+=) x @ w.T + bias.  x [M,K] and w [N,K] of one dtype; bias float32; see EPI_*."""
+                  epilogue: int, act: int = ACT_NONE) -> None:
+    """out (=|+=) x @ w.T + bias.  x [M,K] and w [N,K] of one dtype; bias float32; see EPI_*.  act (EPI_STORE
+    only): the activation applied to what is stored, see ACT_*."""
     _need(x, "x", contiguous=False); _need(w, "w", x.dtype); _need(out, "out", contiguous=False)
     if x.stride(-1) != 1 or out.stride(-1) != 1:
         raise KernelError("linear: rows must be contiguous")
@@ -286,10 +290,11 @@ def linear_simple(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
     want = x.dtype if epilogue == EPI_STORE else torch.float32
     if out.dtype != want:
         raise KernelError(f"linear: epilogue {epilogue} writes {want}, out is {out.dtype}")
-    f = _fn("linear_simple", "stratum_linear_simple",
-            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    f = _fn("linear_simple", "stratum_linear_simple_act",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_void_p])
     _check(f(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), dtype_code(x.dtype), epilogue, M, N, K, x.stride(0),
-             out.stride(0), _stream()), "linear_simple")
+             out.stride(0), act, _stream()), "linear_simple")
 
 
 def linear_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_step: int, o_step: int) -> None:
@@ -324,14 +329,14 @@ def _linear_shapes(x, w, bias, out, epilogue, what):
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-                epilogue: int) -> None:
-    """bfloat16, at most 32 rows of x: the weight-streaming tensor-core kernel (see EPI_*)."""
+                epilogue: int, act: int = ACT_NONE) -> None:
+    """bfloat16, at most 32 rows of x: the weight-streaming tensor-core kernel (see EPI_*; act as linear_simple's)."""
     M, N, Kd = _linear_shapes(x, w, bias, out, epilogue, "gemm_skinny")
     _need(x, "x", torch.bfloat16, contiguous=False)
-    f = _fn("gemm_skinny", "stratum_gemm_skinny",
-            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), epilogue, M, N, Kd, x.stride(0), out.stride(0), _stream()),
-           "gemm_skinny")
+    f = _fn("gemm_skinny", "stratum_gemm_skinny_act",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), epilogue, M, N, Kd, x.stride(0), out.stride(0), act,
+             _stream()), "gemm_skinny")
 
 
 _scratch_epoch = 0
@@ -394,7 +399,7 @@ class _EpiExtra(ctypes.Structure):
                 ("norm_parts", c_int), ("norm_ld", c_int), ("norm_size", c_float), ("norm_eps", c_float),
                 ("emit_ldx", c_int), ("emit_ld", c_int),
                 ("rope_pairs", c_int), ("bt_stride", c_int), ("n_q", c_int), ("n_kv", c_int), ("head_dim", c_int),
-                ("page_tokens", c_int), ("write_cache", c_int), ("reserved", c_int)]
+                ("page_tokens", c_int), ("write_cache", c_int), ("act", c_int)]
 
 
 class GemmExtra:
@@ -406,12 +411,17 @@ class GemmExtra:
                   [parts, rows] the sums of squares of the new residual values per tile of columns (how many
                   parts were written: `last_parts()` after the call);
     EPI_QKV_ROPE  the columns are query, key and value heads (pairs of rotated dimensions neighbours): queries
-                  are rotated and stored to `out`, keys rotated and written, values written, into the paged cache.
+                  are rotated and stored to `out`, keys rotated and written, values written, into the paged cache;
+    activation    EPI_STORE applies ACT_* to what it stores.
     """
 
     def __init__(self):
         self.c = _EpiExtra()
         self.keep = []                      # tensors whose memory the struct points into
+
+    def activation(self, act: int) -> "GemmExtra":
+        self.c.act = int(act)
+        return self
 
     def scaled_rows(self, norm_ss: torch.Tensor, parts: int, size: int, eps: float) -> "GemmExtra":
         _need(norm_ss, "norm_ss", torch.float32)

@@ -70,8 +70,20 @@ def takes_tensor_cores(x: torch.Tensor, w: torch.Tensor, extras: bool) -> bool:
 
 
 def run(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, mode: int,
-        extra=None) -> None:
-    """out (=|+=) epilogue(x @ w.T + bias); see the EPI_* modes in kernels.py."""
+        extra=None, act: int = 0) -> None:
+    """out (=|+=) epilogue(x @ w.T + bias); see the EPI_* modes in kernels.py.  act (STORE only): an activation
+    applied to what is stored (kernels.ACT_*), by whichever kernel takes the call."""
+    if act:
+        if mode != STORE or extra is not None:
+            raise K.KernelError("an activation goes with the plain store epilogue")
+        if x.dtype == torch.bfloat16 and _aligned(x, w):
+            if x.shape[0] <= SKINNY_MAX_ROWS and w.numel() < STREAMK_MIN_WEIGHTS:
+                K.gemm_skinny(x, w, bias, out, mode, act)
+            else:
+                K.gemm_tc(x, w, bias, out, mode, K.GemmExtra().activation(act))
+        else:
+            K.linear_simple(x, w, bias, out, mode, act)
+        return
     if extra is not None:
         if not takes_tensor_cores(x, w, extras=True):
             raise K.KernelError("this product carries epilogue work that only the tensor-core kernel does, and its "

@@ -27,12 +27,14 @@ class Linear:
         self.bias = bias
         self.out_features, self.in_features = weight.shape
 
-    def __call__(self, x, out: Optional[torch.Tensor] = None, mode: int = STORE, emit=None, extra=None) -> torch.Tensor:
+    def __call__(self, x, out: Optional[torch.Tensor] = None, mode: int = STORE, emit=None, extra=None,
+                 act: int = 0) -> torch.Tensor:
         """mode STORE: new tensor of x's dtype; ADD_TO_F32: out (float32) += y; STORE_F32: float32 out;
         SWIGLU: rows of W alternate gate and up, out[m][j] = silu(y[m][2j]) * y[m][2j+1] in x's dtype;
         QKV_ROPE: see kernels.GemmExtra (extra carries the cache and the rotation table; out: the query rows).
         x may be NormedRows (the product then applies the norm's row factors).  emit: a Handover that the
-        ADD_TO_F32 product honours where it can (emit.result is then set)."""
+        ADD_TO_F32 product honours where it can (emit.result is then set).  act (STORE only): an activation the
+        product applies to what it stores (kernels.ACT_*)."""
         from . import gemm_dispatch
         from .base import NormedRows
         normed = x if isinstance(x, NormedRows) else None
@@ -56,7 +58,7 @@ class Linear:
             parts = K.gemm_tc(x, self.weight, self.bias, out, K.EPI_ADD_F32_EMIT, extra)
             emit.result = NormedRows(xb, ss, parts, emit.size, emit.eps)
             return out
-        gemm_dispatch.run(x, self.weight, self.bias, out, mode, extra)
+        gemm_dispatch.run(x, self.weight, self.bias, out, mode, extra, act)
         return out
 
 

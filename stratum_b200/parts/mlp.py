@@ -1,5 +1,6 @@
 """Feed-forwards.
-Dense with a GELU: residual += Wd gelu(Wu xn), the exact (erf) GELU or its tanh form.
+Dense with a GELU: residual += Wd gelu(Wu xn), the exact (erf) GELU or its tanh form, applied to the
+float32 sums of the first product before they are rounded and stored.
 SwiGLU feed-forward: residual += Wd (silu(Wg xn) * (Wu xn))
 (stratum/native/stratum_arch_llama.inc.c:550-555, stratum/native/stratum_engine.h:373-391).
 
@@ -73,7 +74,7 @@ class DenseGelu(FeedForward):
         act = spec.get("activation", "gelu_erf")
         if act not in ("gelu_erf", "gelu_tanh"):
             raise ValueError(f"dense_gelu: activation {act!r} is neither gelu_erf nor gelu_tanh")
-        self.kind = K.GELU_ERF if act == "gelu_erf" else K.GELU_TANH
+        self.act = K.ACT_GELU_ERF if act == "gelu_erf" else K.ACT_GELU_TANH
         self.up_name = self.prefix + spec.get("up", "up")
         self.down_name = self.prefix + spec.get("down", "down")
         self.up: Optional[Linear] = None
@@ -88,6 +89,5 @@ class DenseGelu(FeedForward):
         self.down = Linear(self.runtime, weights[self.down_name])
 
     def forward(self, xn, residual: torch.Tensor, step) -> None:
-        a = self.up(xn, mode=STORE)
-        K.gelu(a, self.kind)
+        a = self.up(xn, mode=STORE, act=self.act)          # the activation rides on the product's epilogue
         self.down(a, out=residual, mode=ADD_TO_F32)

@@ -364,3 +364,26 @@ def test_tensor_core_attention_against_cuda_cores(case):
         assert np.isfinite(a).all()
         # both round their result to bfloat16 once: one unit in the last place of the larger values
         assert np.max(np.abs(a - b)) <= 2 ** -7 * max(1.0, np.max(np.abs(b))), (n_splits, np.max(np.abs(a - b)))
+
+
+@pytest.mark.parametrize("rows,inner,dtype", [(4, 64, "bfloat16"), (200, 64, "bfloat16"), (700, 512, "bfloat16"),
+                                              (9, 70, "bfloat16"), (33, 70, "float32")])
+def test_activation_on_the_product_epilogue(rows, inner, dtype):
+    """gelu(x W^T) by every matrix-product kernel that can carry the activation: the weight-streaming one (few rows),
+    the tcgen05 one, and the CUDA-core one (sizes no vector load divides; float32)."""
+    from stratum_b200 import kernels as K
+    from stratum_b200.parts.base import Runtime
+    from stratum_b200.parts.linear import STORE, Linear
+    rng = np.random.default_rng(rows)
+    dt = torch.float32 if dtype == "float32" else torch.bfloat16
+    x = torch.tensor(rng.normal(size=(rows, inner)), dtype=dt, device="cuda")
+    w = torch.tensor(rng.normal(size=(150, inner)) * 0.3, dtype=dt, device="cuda")
+    lin = Linear(Runtime(dt, "cuda"), w)
+    pre = lin(x, mode=STORE).float().cpu().numpy()
+    for act, ref in ((K.ACT_GELU_ERF, N.gelu_erf),
+                     (K.ACT_GELU_TANH, lambda z: 0.5 * z * (1 + np.tanh(np.sqrt(2 / np.pi) * (z + 0.044715 * z ** 3))))):
+        got = lin(x, mode=STORE, act=act).float().cpu().numpy()
+        exact = ref(x.float().cpu().numpy().astype(np.float64) @ w.float().cpu().numpy().astype(np.float64).T)
+        tol = 1e-5 if dtype == "float32" else 2 ** -8
+        assert np.max(np.abs(got - exact)) <= tol * max(1.0, np.max(np.abs(exact))), (act, np.max(np.abs(got - exact)))
+        assert np.max(np.abs(got - pre)) > 0.1              # and it is not the plain product
