@@ -27,10 +27,10 @@ NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompi
                            "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
 SOURCES = ("elementwise", "linear_simple", "attention_simple", "sampling", "gemm_skinny", "attention_mma",
            "gemm_tc", "attention_tc", "attention_stream", "attention_static", "attention_general", "attention_general_mma",
-           "mixer_prep")
+           "mixer_prep", "head_gemm")
 HEADERS = ("common.cuh",)
 EXTRA_DEPS = {"attention_general": ("attention_general.h",),
-              "attention_general_mma": ("attention_general.h", "mma_common.cuh"),
+              "attention_general_mma": ("attention_general.h", "mma_common.cuh"), "head_gemm": ("mma_common.cuh",),
               "attention_static": ("attention_mma.cu", "attention_static.h", "mma_common.cuh"),   # files a source includes
               "attention_mma": ("mma_common.cuh",), "attention_stream": ("mma_common.cuh", "tc_common.cuh"),
               "gemm_tc": ("tc_common.cuh",), "attention_tc": ("tc_common.cuh",)}

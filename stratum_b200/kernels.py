@@ -311,6 +311,26 @@ def linear_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_step: in
              out.stride(0), x_step, o_step, _stream()), "linear_heads")
 
 
+def head_gemm_ok(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_step: int, o_step: int) -> bool:
+    """Whether the tensor-core form of linear_heads takes this call."""
+    return (x.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.shape[2] % 8 == 0 and x_step % 8 == 0
+            and x.stride(0) % 8 == 0 and o_step % 2 == 0 and out.stride(0) % 2 == 0 and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0 and out.data_ptr() % 4 == 0)
+
+
+def head_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_step: int, o_step: int) -> None:
+    """linear_heads in bfloat16 on tensor cores: every head's product in one launch (see head_gemm_ok)."""
+    _need(x, "x", torch.bfloat16, contiguous=False); _need(w, "w", torch.bfloat16)
+    _need(out, "out", torch.bfloat16, contiguous=False)
+    if x.stride(-1) != 1 or out.stride(-1) != 1 or w.dim() != 3:
+        raise KernelError("head_gemm: rows must be contiguous and w [heads, N, K]")
+    heads, N, Kd = w.shape
+    f = _fn("head_gemm", "stratum_head_gemm",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(w), _ptr(out), heads, x.shape[0], N, Kd, x.stride(0), out.stride(0), x_step, o_step,
+             _stream()), "head_gemm")
+
+
 def _linear_shapes(x, w, bias, out, epilogue, what):
     _need(x, "x", contiguous=False); _need(w, "w", x.dtype); _need(out, "out", contiguous=False)
     if x.stride(-1) != 1 or out.stride(-1) != 1:

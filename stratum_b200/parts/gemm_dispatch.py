@@ -55,11 +55,6 @@ def _aligned(x: torch.Tensor, w: torch.Tensor) -> bool:
     return (k % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def takes_fast_path(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether `run` serves this product with one of the bfloat16 tensor-core kernels."""
-    return x.dtype == torch.bfloat16 and _aligned(x, w)
-
-
 def takes_tensor_cores(x: torch.Tensor, w: torch.Tensor, extras: bool) -> bool:
     """Whether this product goes to gemm_tc.  extras: the call carries work only gemm_tc's epilogues do (rows of
     a handed-over norm, the query/key/value epilogue), which decides where the weight-streaming kernel would

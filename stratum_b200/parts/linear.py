@@ -65,8 +65,8 @@ class Linear:
 class HeadLinear:
     """One matrix per head: out[:, j*o_step : j*o_step+N] = x[:, j*x_step : j*x_step+K] @ weight[j].T.
 
-    weight [heads, N, K].  float32: one launch of the CUDA-core kernel over all heads.  bfloat16: one
-    tensor-core product per head where the views meet those kernels' alignment rules, else the same kernel."""
+    weight [heads, N, K].  One launch over all heads: bfloat16 with sizes in multiples of 8 on tensor cores
+    (head_gemm.cu), everything else on the CUDA cores (the float32 path among it)."""
 
     def __init__(self, runtime: Runtime, weight: torch.Tensor):
         if weight.dim() != 3:
@@ -76,15 +76,10 @@ class HeadLinear:
         self.heads, self.out_features, self.in_features = self.weight.shape
 
     def __call__(self, x: torch.Tensor, x_step: int, out: torch.Tensor, o_step: int) -> torch.Tensor:
-        from . import gemm_dispatch
         if x.shape[0] == 0:
             return out
-        N, Kd = self.out_features, self.in_features
-        views = [(x[:, j * x_step: j * x_step + Kd], self.weight[j], out[:, j * o_step: j * o_step + N])
-                 for j in range(self.heads)]
-        if x.dtype == torch.bfloat16 and all(gemm_dispatch.takes_fast_path(xv, wv) for xv, wv, _ in views):
-            for xv, wv, ov in views:
-                gemm_dispatch.run(xv, wv, None, ov, STORE)
+        if K.head_gemm_ok(x, self.weight, out, x_step, o_step):
+            K.head_gemm(x, self.weight, out, x_step, o_step)
         else:
             K.linear_heads(x, self.weight, out, x_step, o_step)
         return out

@@ -387,3 +387,26 @@ def test_activation_on_the_product_epilogue(rows, inner, dtype):
         tol = 1e-5 if dtype == "float32" else 2 ** -8
         assert np.max(np.abs(got - exact)) <= tol * max(1.0, np.max(np.abs(exact))), (act, np.max(np.abs(got - exact)))
         assert np.max(np.abs(got - pre)) > 0.1              # and it is not the plain product
+
+
+@pytest.mark.parametrize("rows", [1, 8, 20, 33, 300])
+@pytest.mark.parametrize("heads,n,k,x_step,o_step", [(4, 128, 32, 48, 144), (16, 64, 256, 256, 64), (3, 40, 24, 32, 40),
+                                                      (2, 17, 13, 19, 17)])
+def test_per_head_products(rows, heads, n, k, x_step, o_step):
+    """HeadLinear: all heads in one launch, on tensor cores where the sizes allow and on the CUDA cores elsewhere
+    (the last shape), against the definition."""
+    from stratum_b200.parts.base import Runtime
+    from stratum_b200.parts.linear import HeadLinear
+    rng = np.random.default_rng(rows + n)
+    ldx, ldo = (heads * x_step + 7) // 8 * 8, (heads * o_step + 7) // 8 * 8
+    x = torch.tensor(rng.normal(size=(rows, ldx)), dtype=torch.bfloat16, device="cuda")
+    w = torch.tensor(rng.normal(size=(heads, n, k)) * 0.2, dtype=torch.bfloat16, device="cuda")
+    out = torch.full((rows, ldo), 7.0, dtype=torch.bfloat16, device="cuda")
+    HeadLinear(Runtime(torch.bfloat16, "cuda"), w)(x, x_step, out, o_step)
+    xf, wf = x.float().cpu().numpy().astype(np.float64), w.float().cpu().numpy().astype(np.float64)
+    got = out.float().cpu().numpy()
+    for j in range(heads):
+        ref = xf[:, j * x_step: j * x_step + k] @ wf[j].T
+        assert np.max(np.abs(got[:, j * o_step: j * o_step + n] - ref)) <= 2 ** -8 * max(1.0, np.max(np.abs(ref)))
+    if o_step > n:                                         # columns between the heads' results are left alone
+        assert np.all(got[:, n:o_step] == 7.0)
