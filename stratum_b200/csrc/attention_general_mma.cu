@@ -1,8 +1,9 @@
 // The general attention (attention_general.cu) in bfloat16 on tensor cores, for prompts and for decode steps.
 //
-// A CTA of four warps owns one work item: up to 16 query rows that share their keys (consecutive new tokens of a
-// sequence x the heads of one key/value group, for one score map) and one contiguous range of that sequence's
-// keys.  Keys are visited in tiles of 64 (one page).  Per tile:
+// A CTA of four warps owns one work item: up to RG groups of 16 query rows that share their keys (consecutive new
+// tokens of a sequence x the heads of one key/value group, for one score map) and one contiguous range of that
+// sequence's keys.  Keys are visited in tiles of 64 (one page); the groups take every tile in turn, so that the
+// tile's keys and values come from L2 once and from L1 afterwards.  Per tile and group:
 //   scores   warp w computes the 16 x 16 block of rows x keys 16w..16w+15: mma.sync.m16n8k16 over the key
 //            dimension, Q fragments from shared memory, K fragments straight from the cache rows (a dot product
 //            may visit the dimension in any order as long as Q and K agree: lane t of a row takes the 8
@@ -26,7 +27,9 @@
 #define GM_TILE 64
 #define GM_PSTRIDE 72          // bf16 per row of the probability tiles: 64 keys + 8 of padding (no bank conflicts)
 
-__device__ __forceinline__ uint4 gm_ldg16(const void* p) { return ld_fresh((const uint4*)p); }
+// this kernel is launched the ordinary way: it starts when the kernels before it have ended, so plain loads (which
+// may be served by L1) see what they wrote
+__device__ __forceinline__ uint4 gm_ldg16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
 
 __host__ __device__ __forceinline__ int gm_q_stride(int D) {       // bytes per row of Q in shared memory: = 64 mod 128
   int s = ((D * 2 + 15) / 16) * 16;
@@ -34,7 +37,7 @@ __host__ __device__ __forceinline__ int gm_q_stride(int D) {       // bytes per 
   return s;
 }
 
-template <int CPW>
+template <int CPW, int RG>
 __global__ void __launch_bounds__(GM_WARPS * 32)
 attention_general_mma_kernel(const GeneralAttention P) {
   extern __shared__ __align__(16) unsigned char gm_smem[];
@@ -42,8 +45,8 @@ attention_general_mma_kernel(const GeneralAttention P) {
   const int g = lane >> 2, t = lane & 3;
   const int D = P.qk_dim, Dv = P.v_dim;
   const int qstride = gm_q_stride(D);
-  unsigned char* q_s = gm_smem;                                                  // [16][qstride bytes]
-  bf16* p_hi = reinterpret_cast<bf16*>(gm_smem + 16 * qstride);                  // [16][GM_PSTRIDE]
+  unsigned char* q_s = gm_smem;                                                  // [RG][16][qstride bytes]
+  bf16* p_hi = reinterpret_cast<bf16*>(gm_smem + RG * 16 * qstride);             // [16][GM_PSTRIDE]
   bf16* p_lo = p_hi + 16 * GM_PSTRIDE;
   float* max_s = reinterpret_cast<float*>(p_lo + 16 * GM_PSTRIDE);               // [GM_WARPS][16]
   float* sum_s = max_s + GM_WARPS * 16;                                          // [GM_WARPS][16]
@@ -61,23 +64,28 @@ attention_general_mma_kernel(const GeneralAttention P) {
   if (seq < 0) return;                                                           // padding
   const int tok0 = P.qb_tok0 ? P.qb_tok0[qb] : qb;
   const int ntok = P.qb_ntok ? P.qb_ntok[qb] : 1;
+  const int tpg = P.tokens_per_block;                                            // tokens of one group of 16 rows
 
-  // the two rows of this lane: r = g and g + 8;  row -> (token of the block, head of the group)
-  int row_tok[2], row_head[2], row_pos[2];
-  bool row_ok[2];
-  float row_factor[2];
+  // the two rows of this lane in every group of 16 rows: r = g and g + 8;  row -> (token of the group, head)
+  int row_tok[RG][2], row_head[2], row_pos[RG][2];
+  bool row_ok[RG][2];
+  float row_factor[RG][2];
 #pragma unroll
   for (int e = 0; e < 2; e++) {
     const int r = g + 8 * e;
     const int tr = r / rows_per_token, hr = r % rows_per_token;
     const int hq = hg * 16 + hr;
-    row_ok[e] = tr < ntok && tr < P.tokens_per_block && hq < P.group;
-    row_tok[e] = tok0 + (row_ok[e] ? tr : 0);
-    row_head[e] = kv * P.group + (row_ok[e] ? hq : 0);
-    row_pos[e] = P.token_pos[row_tok[e]];
-    float temp = 1.f;
-    if (P.temp_coef != 0.f) temp = 1.f + P.temp_coef * logf((float)((row_pos[e] + 1) / P.temp_every) + 1.f);
-    row_factor[e] = P.scale * temp;
+    row_head[e] = kv * P.group + (hq < P.group ? hq : 0);
+#pragma unroll
+    for (int rg = 0; rg < RG; rg++) {
+      const int tk = rg * tpg + tr;
+      row_ok[rg][e] = tr < tpg && tk < ntok && hq < P.group;
+      row_tok[rg][e] = tok0 + (row_ok[rg][e] ? tk : 0);
+      row_pos[rg][e] = P.token_pos[row_tok[rg][e]];
+      float temp = 1.f;
+      if (P.temp_coef != 0.f) temp = 1.f + P.temp_coef * logf((float)((row_pos[rg][e] + 1) / P.temp_every) + 1.f);
+      row_factor[rg][e] = P.scale * temp;
+    }
   }
   const int first_pos = P.token_pos[tok0];
   const int last_pos = first_pos + ntok - 1;
@@ -90,15 +98,16 @@ attention_general_mma_kernel(const GeneralAttention P) {
   // Q rows of this item into shared memory (16 bytes per thread and turn; rows that do not exist are zero)
   {
     const int pieces = D / 8;
-    for (int i = threadIdx.x; i < 16 * pieces; i += blockDim.x) {
+    for (int i = threadIdx.x; i < RG * 16 * pieces; i += blockDim.x) {
       const int r = i / pieces, c = i - r * pieces;
-      const int tr = r / rows_per_token, hr = r % rows_per_token;
-      const int hq = hg * 16 + hr;
-      const bool ok = tr < ntok && tr < P.tokens_per_block && hq < P.group;
+      const int rg = r / 16, rr = r % 16;
+      const int tr = rr / rows_per_token, hr = rr % rows_per_token;
+      const int hq = hg * 16 + hr, tk = rg * tpg + tr;
+      const bool ok = tr < tpg && tk < ntok && hq < P.group;
       uint4 v = make_uint4(0, 0, 0, 0);
       if (ok)
-        v = gm_ldg16((const bf16*)P.q + (size_t)(tok0 + tr) * P.ldq +
-                     ((size_t)(kv * P.group + hq) * P.maps + map) * D + 8 * c);
+        v = ld_fresh((const uint4*)((const bf16*)P.q + (size_t)(tok0 + tk) * P.ldq +
+                                    ((size_t)(kv * P.group + hq) * P.maps + map) * D + 8 * c));
       *reinterpret_cast<uint4*>(q_s + (size_t)r * qstride + 16 * c) = v;
     }
   }
@@ -113,228 +122,281 @@ attention_general_mma_kernel(const GeneralAttention P) {
   const int n_kc = (D + 31) / 32;                 // chunks of the key dimension
   const int n_vc = (Dv + 31) / 32;                // chunks of the value dimension
 
-  float o[CPW * 4][4];
+  float o[RG][CPW * 4][4];
+  float m_run[RG][2], l_run[RG][2];
 #pragma unroll
-  for (int i = 0; i < CPW * 4; i++) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  for (int rg = 0; rg < RG; rg++) {
+#pragma unroll
+    for (int i = 0; i < CPW * 4; i++) { o[rg][i][0] = o[rg][i][1] = o[rg][i][2] = o[rg][i][3] = 0.f; }
+    m_run[rg][0] = m_run[rg][1] = -INFINITY;
+    l_run[rg][0] = l_run[rg][1] = 0.f;
+  }
   const uint4 zero4 = make_uint4(0, 0, 0, 0);
 
   for (int key0 = (k_begin / GM_TILE) * GM_TILE; key0 < k_end; key0 += GM_TILE) {
     const int page = bt[key0 / P.page_tokens];
     const int in_page = key0 % P.page_tokens;
-    // ---- scores of keys key0 + 16 warp + [0, 16)
     const int kw = key0 + 16 * warp;
-    float s[2][4];
+    const bf16* kr = (const bf16*)P.k_cache + (size_t)page * k_page + k_head + (size_t)(in_page + 16 * warp) * D;
+    const bf16* vr = v_base + (size_t)page * v_page + v_head + (size_t)in_page * v_row;
 #pragma unroll
-    for (int i = 0; i < 2; i++) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
-    const bool any = kw < k_end && kw + 15 >= k_begin;
-    if (any) {
-      const bf16* kr = (const bf16*)P.k_cache + (size_t)page * k_page + k_head + (size_t)(in_page + 16 * warp) * D;
+    for (int rg = 0; rg < RG; rg++) {
+      // the last position of this group of rows (the same for every thread of the CTA)
+      const int g_first = first_pos + rg * tpg;
+      if (rg > 0 && (rg * tpg >= ntok || key0 > min(g_first + tpg - 1, last_pos))) continue;
+      const int g_end = min(k_end, min(g_first + tpg - 1, last_pos) + 1);      // keys this group can see end here
+      // ---- scores of keys key0 + 16 warp + [0, 16)
+      float s[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; i++) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+      const bool any = kw < g_end && kw + 15 >= k_begin;
+      if (any) {
+        const unsigned char* qg = q_s + (size_t)rg * 16 * qstride;
 #pragma unroll 4
-      for (int c = 0; c < n_kc; c++) {
+        for (int c = 0; c < n_kc; c++) {
+          const int d = 32 * c + 8 * t;
+          const bool d_ok = d < D;
+          const uint4 ka = d_ok ? gm_ldg16(kr + (size_t)g * D + d) : zero4;
+          const uint4 kb = d_ok ? gm_ldg16(kr + (size_t)(g + 8) * D + d) : zero4;
+          const uint4 qa = d_ok ? *reinterpret_cast<const uint4*>(qg + (size_t)g * qstride + 2 * d) : zero4;
+          const uint4 qc = d_ok ? *reinterpret_cast<const uint4*>(qg + (size_t)(g + 8) * qstride + 2 * d) : zero4;
+          mma16816(s[0], qa.x, qc.x, qa.y, qc.y, ka.x, ka.y);
+          mma16816(s[0], qa.z, qc.z, qa.w, qc.w, ka.z, ka.w);
+          mma16816(s[1], qa.x, qc.x, qa.y, qc.y, kb.x, kb.y);
+          mma16816(s[1], qa.z, qc.z, qa.w, qc.w, kb.z, kb.w);
+        }
+      }
+      float bm[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          const int e = j >> 1;
+          const int key = kw + 8 * i + 2 * t + (j & 1);
+          const int pos = row_pos[rg][e];
+          const int lo = (P.window > 0 && pos - P.window + 1 > 0) ? pos - P.window + 1 : 0;
+          const bool ok = any && row_ok[rg][e] && key <= pos && key >= lo && key < k_end && key >= k_begin;
+          float v = s[i][j] * row_factor[rg][e];
+          if (P.softcap > 0.f) v = P.softcap * tanhf(v / P.softcap);
+          s[i][j] = ok ? v : -INFINITY;
+          bm[e] = fmaxf(bm[e], s[i][j]);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 1));
+        bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 2));
+        if (t == 0) max_s[warp * 16 + g + 8 * e] = bm[e];
+      }
+      __syncthreads();
+      float corr[2], m_use[2];
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        const int r = g + 8 * e;
+        const float tile_max = fmaxf(fmaxf(max_s[r], max_s[16 + r]), fmaxf(max_s[32 + r], max_s[48 + r]));
+        const float m_new = fmaxf(m_run[rg][e], tile_max);
+        m_use[e] = (m_new == -INFINITY) ? 0.f : m_new;      // a row with no key yet: exponents of -inf give 0
+        corr[e] = expf(m_run[rg][e] - m_use[e]);            // first keys: exp(-inf) = 0
+        m_run[rg][e] = m_new;
+      }
+      float psum[2] = {0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+          const float p0 = expf(s[i][2 * e] - m_use[e]), p1 = expf(s[i][2 * e + 1] - m_use[e]);
+          psum[e] += p0 + p1;
+          const __nv_bfloat162 hi = __floats2bfloat162_rn(p0, p1);
+          const __nv_bfloat162 lo = __floats2bfloat162_rn(p0 - __bfloat162float(hi.x), p1 - __bfloat162float(hi.y));
+          const int at = (g + 8 * e) * GM_PSTRIDE + 16 * warp + 8 * i + 2 * t;
+          *reinterpret_cast<__nv_bfloat162*>(p_hi + at) = hi;
+          *reinterpret_cast<__nv_bfloat162*>(p_lo + at) = lo;
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 2; e++) l_run[rg][e] = l_run[rg][e] * corr[e] + psum[e];
+      __syncthreads();
+      // ---- values: chunks of 32 dimensions c = warp, warp + 4, ...
+#pragma unroll
+      for (int i = 0; i < CPW * 4; i++) {
+        o[rg][i][0] *= corr[0]; o[rg][i][1] *= corr[0]; o[rg][i][2] *= corr[1]; o[rg][i][3] *= corr[1];
+      }
+      const int blocks = min(GM_TILE, g_end - key0 + 15) / 16;        // blocks of 16 keys that hold a key
+#pragma unroll
+      for (int cc = 0; cc < CPW; cc++) {
+        const int c = warp + GM_WARPS * cc;
         const int d = 32 * c + 8 * t;
-        const bool d_ok = d < D;
-        const uint4 ka = d_ok ? gm_ldg16(kr + (size_t)g * D + d) : zero4;
-        const uint4 kb = d_ok ? gm_ldg16(kr + (size_t)(g + 8) * D + d) : zero4;
-        const uint4 qa = d_ok ? *reinterpret_cast<const uint4*>(q_s + (size_t)g * qstride + 2 * d) : zero4;
-        const uint4 qc = d_ok ? *reinterpret_cast<const uint4*>(q_s + (size_t)(g + 8) * qstride + 2 * d) : zero4;
-        mma16816(s[0], qa.x, qc.x, qa.y, qc.y, ka.x, ka.y);
-        mma16816(s[0], qa.z, qc.z, qa.w, qc.w, ka.z, ka.w);
-        mma16816(s[1], qa.x, qc.x, qa.y, qc.y, kb.x, kb.y);
-        mma16816(s[1], qa.z, qc.z, qa.w, qc.w, kb.z, kb.w);
-      }
-    }
-    float bm[2] = {-INFINITY, -INFINITY};
+        if (c >= n_vc) break;
+        // all of the tile's loads of this chunk first, so that their latencies overlap
+        uint4 va[GM_TILE / 16], vb[GM_TILE / 16];
 #pragma unroll
-    for (int i = 0; i < 2; i++) {
+        for (int kb = 0; kb < GM_TILE / 16; kb++) {
+          const bool ok = kb < blocks && d < Dv;
+          va[kb] = ok ? gm_ldg16(vr + (size_t)(16 * kb + g) * v_row + d) : zero4;
+          vb[kb] = ok ? gm_ldg16(vr + (size_t)(16 * kb + 8 + g) * v_row + d) : zero4;
+        }
 #pragma unroll
-      for (int j = 0; j < 4; j++) {
-        const int e = j >> 1;
-        const int key = kw + 8 * i + 2 * t + (j & 1);
-        const int lo = (P.window > 0 && row_pos[e] - P.window + 1 > 0) ? row_pos[e] - P.window + 1 : 0;
-        const bool ok = any && row_ok[e] && key <= row_pos[e] && key >= lo && key < k_end && key >= k_begin;
-        float v = s[i][j] * row_factor[e];
-        if (P.softcap > 0.f) v = P.softcap * tanhf(v / P.softcap);
-        s[i][j] = ok ? v : -INFINITY;
-        bm[e] = fmaxf(bm[e], s[i][j]);
+        for (int kb = 0; kb < GM_TILE / 16; kb++) {
+          if (kb >= blocks) break;
+          const int a_at = g * GM_PSTRIDE + 16 * kb + 2 * t;
+          const uint32_t h0 = *reinterpret_cast<const uint32_t*>(p_hi + a_at);
+          const uint32_t h1 = *reinterpret_cast<const uint32_t*>(p_hi + a_at + 8 * GM_PSTRIDE);
+          const uint32_t h2 = *reinterpret_cast<const uint32_t*>(p_hi + a_at + 8);
+          const uint32_t h3 = *reinterpret_cast<const uint32_t*>(p_hi + a_at + 8 * GM_PSTRIDE + 8);
+          const uint32_t l0 = *reinterpret_cast<const uint32_t*>(p_lo + a_at);
+          const uint32_t l1 = *reinterpret_cast<const uint32_t*>(p_lo + a_at + 8 * GM_PSTRIDE);
+          const uint32_t l2 = *reinterpret_cast<const uint32_t*>(p_lo + a_at + 8);
+          const uint32_t l3 = *reinterpret_cast<const uint32_t*>(p_lo + a_at + 8 * GM_PSTRIDE + 8);
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            const uint32_t b0 = transpose8x8(reg_of(va[kb], i));
+            const uint32_t b1 = transpose8x8(reg_of(vb[kb], i));
+            mma16816(o[rg][4 * cc + i], h0, h1, h2, h3, b0, b1);
+            mma16816(o[rg][4 * cc + i], l0, l1, l2, l3, b0, b1);
+          }
+        }
       }
+      __syncthreads();                             // the tiles of probabilities and the maxima are written again
     }
+  }
+
+  const bool direct = P.n_splits == 1 && P.combine == 0;
+#pragma unroll
+  for (int rg = 0; rg < RG; rg++) {
+    if (rg > 0 && rg * tpg >= ntok) break;
+    // denominators: across the four lanes of a row, then across the warps
+    float l_all[2];
 #pragma unroll
     for (int e = 0; e < 2; e++) {
-      bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 1));
-      bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 2));
-      if (t == 0) max_s[warp * 16 + g + 8 * e] = bm[e];
+      float l = l_run[rg][e];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      if (t == 0) sum_s[warp * 16 + g + 8 * e] = l;
     }
     __syncthreads();
-    float corr[2], m_use[2];
 #pragma unroll
     for (int e = 0; e < 2; e++) {
       const int r = g + 8 * e;
-      const float tile_max = fmaxf(fmaxf(max_s[r], max_s[16 + r]), fmaxf(max_s[32 + r], max_s[48 + r]));
-      const float m_new = fmaxf(m_run[e], tile_max);
-      m_use[e] = (m_new == -INFINITY) ? 0.f : m_new;      // a row with no key yet: exponents of -inf give 0
-      corr[e] = expf(m_run[e] - m_use[e]);                // first keys: exp(-inf) = 0
-      m_run[e] = m_new;
+      l_all[e] = (sum_s[r] + sum_s[16 + r]) + (sum_s[32 + r] + sum_s[48 + r]);
     }
-    float psum[2] = {0.f, 0.f};
-#pragma unroll
-    for (int i = 0; i < 2; i++) {
-#pragma unroll
-      for (int e = 0; e < 2; e++) {
-        const float p0 = expf(s[i][2 * e] - m_use[e]), p1 = expf(s[i][2 * e + 1] - m_use[e]);
-        psum[e] += p0 + p1;
-        const __nv_bfloat162 hi = __floats2bfloat162_rn(p0, p1);
-        const __nv_bfloat162 lo = __floats2bfloat162_rn(p0 - __bfloat162float(hi.x), p1 - __bfloat162float(hi.y));
-        const int at = (g + 8 * e) * GM_PSTRIDE + 16 * warp + 8 * i + 2 * t;
-        *reinterpret_cast<__nv_bfloat162*>(p_hi + at) = hi;
-        *reinterpret_cast<__nv_bfloat162*>(p_lo + at) = lo;
-      }
-    }
-#pragma unroll
-    for (int e = 0; e < 2; e++) l_run[e] = l_run[e] * corr[e] + psum[e];
     __syncthreads();
-    // ---- values: chunks of 32 dimensions c = warp, warp + 4, ...
 #pragma unroll
-    for (int i = 0; i < CPW * 4; i++) {
-      o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
-    }
-    const bf16* vr = v_base + (size_t)page * v_page + v_head + (size_t)in_page * v_row;
-    const int blocks = min(GM_TILE, k_end - key0 + 15) / 16;          // blocks of 16 keys that hold a key
+    for (int e = 0; e < 2; e++) {
+      if (!row_ok[rg][e]) continue;
+      if (direct) {
+        const float inv = 1.0f / l_all[e];
+        bf16* op = (bf16*)P.out + (size_t)row_tok[rg][e] * P.ldo + (size_t)row_head[e] * Dv;
 #pragma unroll
-    for (int cc = 0; cc < CPW; cc++) {
-      const int c = warp + GM_WARPS * cc;
-      const int d = 32 * c + 8 * t;
-      if (c >= n_vc) break;
-      for (int kb = 0; kb < blocks; kb++) {
-        const uint4 va = d < Dv ? gm_ldg16(vr + (size_t)(16 * kb + g) * v_row + d) : zero4;
-        const uint4 vb = d < Dv ? gm_ldg16(vr + (size_t)(16 * kb + 8 + g) * v_row + d) : zero4;
-        const int a_at = g * GM_PSTRIDE + 16 * kb + 2 * t;
-        const uint32_t h0 = *reinterpret_cast<const uint32_t*>(p_hi + a_at);
-        const uint32_t h1 = *reinterpret_cast<const uint32_t*>(p_hi + a_at + 8 * GM_PSTRIDE);
-        const uint32_t h2 = *reinterpret_cast<const uint32_t*>(p_hi + a_at + 8);
-        const uint32_t h3 = *reinterpret_cast<const uint32_t*>(p_hi + a_at + 8 * GM_PSTRIDE + 8);
-        const uint32_t l0 = *reinterpret_cast<const uint32_t*>(p_lo + a_at);
-        const uint32_t l1 = *reinterpret_cast<const uint32_t*>(p_lo + a_at + 8 * GM_PSTRIDE);
-        const uint32_t l2 = *reinterpret_cast<const uint32_t*>(p_lo + a_at + 8);
-        const uint32_t l3 = *reinterpret_cast<const uint32_t*>(p_lo + a_at + 8 * GM_PSTRIDE + 8);
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-          const uint32_t b0 = transpose8x8(reg_of(va, i));
-          const uint32_t b1 = transpose8x8(reg_of(vb, i));
-          mma16816(o[4 * cc + i], h0, h1, h2, h3, b0, b1);
-          mma16816(o[4 * cc + i], l0, l1, l2, l3, b0, b1);
+        for (int cc = 0; cc < CPW; cc++) {
+          const int d = 32 * (warp + GM_WARPS * cc) + 8 * t;
+          if (d >= Dv) continue;
+          uint4 v;
+          v.x = pack_bf16(o[rg][4 * cc + 0][2 * e] * inv, o[rg][4 * cc + 0][2 * e + 1] * inv);
+          v.y = pack_bf16(o[rg][4 * cc + 1][2 * e] * inv, o[rg][4 * cc + 1][2 * e + 1] * inv);
+          v.z = pack_bf16(o[rg][4 * cc + 2][2 * e] * inv, o[rg][4 * cc + 2][2 * e + 1] * inv);
+          v.w = pack_bf16(o[rg][4 * cc + 3][2 * e] * inv, o[rg][4 * cc + 3][2 * e + 1] * inv);
+          *reinterpret_cast<uint4*>(op + d) = v;
         }
-      }
-    }
-    __syncthreads();                               // the tiles of probabilities and the maxima are written again
-  }
-
-  // denominators: across the four lanes of a row, then across the warps
+      } else {
+        const size_t slot = (((size_t)row_tok[rg][e] * P.n_heads + row_head[e]) * P.maps + map) * P.n_splits + split;
+        float* po = P.part_o + slot * Dv;
 #pragma unroll
-  for (int e = 0; e < 2; e++) {
-    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 1);
-    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 2);
-    if (t == 0) sum_s[warp * 16 + g + 8 * e] = l_run[e];
-  }
-  __syncthreads();
-#pragma unroll
-  for (int e = 0; e < 2; e++) {
-    const int r = g + 8 * e;
-    l_run[e] = (sum_s[r] + sum_s[16 + r]) + (sum_s[32 + r] + sum_s[48 + r]);
-  }
-  const bool direct = P.n_splits == 1 && P.combine == 0;
-#pragma unroll
-  for (int e = 0; e < 2; e++) {
-    if (!row_ok[e]) continue;
-    if (direct) {
-      const float inv = 1.0f / l_run[e];
-      bf16* op = (bf16*)P.out + (size_t)row_tok[e] * P.ldo + (size_t)row_head[e] * Dv;
-#pragma unroll
-      for (int cc = 0; cc < CPW; cc++) {
-        const int d = 32 * (warp + GM_WARPS * cc) + 8 * t;
-        if (d >= Dv) continue;
-        uint4 v;
-        v.x = pack_bf16(o[4 * cc + 0][2 * e] * inv, o[4 * cc + 0][2 * e + 1] * inv);
-        v.y = pack_bf16(o[4 * cc + 1][2 * e] * inv, o[4 * cc + 1][2 * e + 1] * inv);
-        v.z = pack_bf16(o[4 * cc + 2][2 * e] * inv, o[4 * cc + 2][2 * e + 1] * inv);
-        v.w = pack_bf16(o[4 * cc + 3][2 * e] * inv, o[4 * cc + 3][2 * e + 1] * inv);
-        *reinterpret_cast<uint4*>(op + d) = v;
-      }
-    } else {
-      const size_t slot = (((size_t)row_tok[e] * P.n_heads + row_head[e]) * P.maps + map) * P.n_splits + split;
-      float* po = P.part_o + slot * Dv;
-#pragma unroll
-      for (int cc = 0; cc < CPW; cc++) {
-        const int d = 32 * (warp + GM_WARPS * cc) + 8 * t;
-        if (d >= Dv) continue;
-        *reinterpret_cast<float4*>(po + d) = make_float4(o[4 * cc + 0][2 * e], o[4 * cc + 0][2 * e + 1],
-                                                         o[4 * cc + 1][2 * e], o[4 * cc + 1][2 * e + 1]);
-        *reinterpret_cast<float4*>(po + d + 4) = make_float4(o[4 * cc + 2][2 * e], o[4 * cc + 2][2 * e + 1],
-                                                             o[4 * cc + 3][2 * e], o[4 * cc + 3][2 * e + 1]);
-      }
-      if (warp == 0 && t == 0) {
-        P.part_ml[slot * 2] = m_run[e];
-        P.part_ml[slot * 2 + 1] = l_run[e];
+        for (int cc = 0; cc < CPW; cc++) {
+          const int d = 32 * (warp + GM_WARPS * cc) + 8 * t;
+          if (d >= Dv) continue;
+          *reinterpret_cast<float4*>(po + d) = make_float4(o[rg][4 * cc + 0][2 * e], o[rg][4 * cc + 0][2 * e + 1],
+                                                           o[rg][4 * cc + 1][2 * e], o[rg][4 * cc + 1][2 * e + 1]);
+          *reinterpret_cast<float4*>(po + d + 4) = make_float4(o[rg][4 * cc + 2][2 * e], o[rg][4 * cc + 2][2 * e + 1],
+                                                               o[rg][4 * cc + 3][2 * e], o[rg][4 * cc + 3][2 * e + 1]);
+        }
+        if (warp == 0 && t == 0) {
+          P.part_ml[slot * 2] = m_run[rg][e];
+          P.part_ml[slot * 2 + 1] = l_all[e];
+        }
       }
     }
   }
 }
 
-// Merge the key ranges of every (token, head, map) in range order, then combine the maps; one warp per
-// (token, head).  A range that held no key of a row left maximum -inf and sum 0 and drops out.
+// Merge the key ranges of every (token, head, map) in range order, then combine the maps; one block per
+// (token, head), one thread per value dimension.  A range that held no key of a row left maximum -inf and sum 0
+// and drops out.
+#define GM_MAX_SPLITS 64
 template <int MAPS>
 __global__ void __launch_bounds__(128) attention_general_finish_kernel(const GeneralAttention P) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * 4 + warp;
-  if (item >= (long long)P.n_tokens * P.n_heads) return;
-  const int tok = (int)(item / P.n_heads), h = (int)(item - (long long)tok * P.n_heads);
+  __shared__ float weight[MAPS][GM_MAX_SPLITS];
+  __shared__ float scratch[33];
+  const int item = blockIdx.x;
+  const int tok = item / P.n_heads, h = item - tok * P.n_heads;
   if (P.token_seq[tok] < 0) return;
-  const int Dv = P.v_dim;
+  const int Dv = P.v_dim, S = P.n_splits;
+  if (threadIdx.x < MAPS) {
+    const int m = threadIdx.x;
+    const float* ml = P.part_ml + ((size_t)item * MAPS + m) * S * 2;
+    float mx = -INFINITY;
+    for (int s = 0; s < S; s++) mx = fmaxf(mx, ml[2 * s]);
+    float l = 0.f;
+    for (int s = 0; s < S; s++) {
+      const float w = ml[2 * s] == -INFINITY ? 0.f : expf(ml[2 * s] - mx);
+      weight[m][s] = w;
+      l += ml[2 * s + 1] * w;
+    }
+    const float inv = 1.0f / l;
+    for (int s = 0; s < S; s++) weight[m][s] *= inv;
+  }
+  __syncthreads();
   bf16* op = (bf16*)P.out + (size_t)tok * P.ldo + (size_t)h * Dv;
-  float ss = 0.f;
-  for (int d0 = 0; d0 < Dv; d0 += 32) {
-    const int d = d0 + lane;
+  float o[4], ss = 0.f;                              // v_dim <= 512: at most four dimensions per thread
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int d = threadIdx.x + 128 * i;
+    o[i] = 0.f;
+    if (d >= Dv) continue;
     float a[MAPS];
 #pragma unroll
     for (int m = 0; m < MAPS; m++) {
-      const size_t slot0 = ((size_t)item * MAPS + m) * P.n_splits;
-      float mx = -INFINITY;
-      for (int s = 0; s < P.n_splits; s++) mx = fmaxf(mx, P.part_ml[(slot0 + s) * 2]);
-      float l = 0.f, acc = 0.f;
-      for (int s = 0; s < P.n_splits; s++) {
-        const float ms = P.part_ml[(slot0 + s) * 2];
-        if (ms == -INFINITY) continue;
-        const float w = expf(ms - mx);
-        l += P.part_ml[(slot0 + s) * 2 + 1] * w;
-        if (d < Dv) acc += P.part_o[(slot0 + s) * Dv + d] * w;
-      }
-      a[m] = acc / l;
+      const float* po = P.part_o + ((size_t)item * MAPS + m) * S * Dv + d;
+      float acc = 0.f;
+#pragma unroll 4
+      for (int s = 0; s < S; s++) acc = fmaf(po[(size_t)s * Dv], weight[m][s], acc);
+      a[m] = acc;
     }
     if (MAPS == 1) {
-      if (d < Dv) op[d] = __float2bfloat16_rn(a[0]);
+      op[d] = __float2bfloat16_rn(a[0]);
     } else {
-      const float o = d < Dv ? a[0] - P.lambda * a[MAPS - 1] : 0.f;
-      ss = fmaf(o, o, ss);
-      if (d < Dv) P.part_o[(size_t)item * MAPS * P.n_splits * Dv + d] = o;     // this row's own scratch, read below
+      o[i] = a[0] - P.lambda * a[MAPS - 1];
+      ss = fmaf(o[i], o[i], ss);
     }
   }
   if (MAPS == 1) return;
-  ss = warp_sum(ss);
+  ss = block_sum(ss, scratch);
   float mul = P.out_scale / sqrtf(ss / (float)Dv + P.eps);
   if (P.gate_col >= 0) {
     const float z = ld_fresh((const bf16*)P.q + (size_t)tok * P.ldq + P.gate_col + h);
     mul *= 1.0f / (1.0f + expf(-z));
   }
-  __syncwarp();
-  for (int d = lane; d < Dv; d += 32)
-    op[d] = __float2bfloat16_rn(P.part_o[(size_t)item * MAPS * P.n_splits * Dv + d] * mul);
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int d = threadIdx.x + 128 * i;
+    if (d < Dv) op[d] = __float2bfloat16_rn(o[i] * mul);
+  }
 }
 
-STRATUM_EXPORT long long stratum_attention_general_mma_smem(int qk_dim) {
-  return 16LL * gm_q_stride(qk_dim) + 2LL * 16 * GM_PSTRIDE * sizeof(bf16) + 2LL * GM_WARPS * 16 * sizeof(float);
+STRATUM_EXPORT long long stratum_attention_general_mma_smem(int qk_dim, int row_groups) {
+  return 16LL * row_groups * gm_q_stride(qk_dim) + 2LL * 16 * GM_PSTRIDE * sizeof(bf16) + 2LL * GM_WARPS * 16 * sizeof(float);
 }
 
-// q, the caches and out bfloat16.  Needs qk_dim % 8 == 0, v_dim % 8 == 0 (v_dim % 32 == 0 when results go through
+// Groups of 16 rows a CTA takes for a value size (prompts): what the host cuts its query blocks by.
+STRATUM_EXPORT int stratum_attention_general_mma_row_groups(int v_dim) {
+  // Measured on 2,048-token prompts with 4 (2 for values of more than 256) groups: 2.96 against 1.74 ms over four
+  // layers of a 2,048-wide model, 8.1 against 5.9 ms of a 4,096-wide one.  The accumulators of several groups
+  // cost more in CTAs per SM than the tiles' second and third readings, which L2 serves, cost in time.  So: one.
+  (void)v_dim;
+  return 1;
+}
+
+// q, the caches and out bfloat16.  `reserved` in the parameters: groups of 16 rows per query block (0 or 1: one;
+// else what stratum_attention_general_mma_row_groups gives).  Needs qk_dim % 8 == 0, v_dim % 8 == 0 (v_dim % 32 == 0 when results go through
 // scratch is not needed: rows of scratch are v_dim floats and v_dim % 8 == 0 keeps them 16-byte aligned), rows of
 // q and out 16-byte aligned, pages of 64 tokens.
 STRATUM_EXPORT int stratum_attention_general_mma(const GeneralAttention* params, cudaStream_t stream) {
@@ -346,20 +408,23 @@ STRATUM_EXPORT int stratum_attention_general_mma(const GeneralAttention* params,
     return STRATUM_ERR_SHAPE;
   if ((((uintptr_t)P.q | (uintptr_t)P.out | (uintptr_t)P.k_cache | (uintptr_t)P.v_cache) & 15) != 0)
     return STRATUM_ERR_ALIGN;
-  if (P.n_splits < 1 || P.chunk < GM_TILE || P.chunk % GM_TILE != 0 || P.tokens_per_block < 1) return STRATUM_ERR_SHAPE;
+  if (P.n_splits < 1 || P.n_splits > GM_MAX_SPLITS || P.v_dim > 512 || P.chunk < GM_TILE || P.chunk % GM_TILE != 0 || P.tokens_per_block < 1) return STRATUM_ERR_SHAPE;
   const bool direct = P.n_splits == 1 && P.combine == 0;
   if (!direct && (!P.part_o || !P.part_ml)) return STRATUM_ERR_SHAPE;
   const int n_vc = (P.v_dim + 31) / 32;
   const int cpw = (n_vc + GM_WARPS - 1) / GM_WARPS;
-  const size_t smem = (size_t)stratum_attention_general_mma_smem(P.qk_dim);
+  // groups of 16 rows per CTA: as many as the accumulators leave registers for (prompts; decode steps have one)
+  const int rg = P.reserved <= 1 ? 1 : P.reserved;
+  if (rg != 1) return STRATUM_ERR_SHAPE;          // the kernel is written for RG groups; only RG = 1 is built (see above)
+  const size_t smem = (size_t)stratum_attention_general_mma_smem(P.qk_dim, rg);
   if (smem > 200 * 1024) return STRATUM_ERR_LIMIT;
   const int head_groups = (P.group + 15) / 16;
   const long long items = (long long)P.n_qblocks * (P.n_heads / P.group) * head_groups * P.maps * P.n_splits;
   if (items > 0x7fffffffLL) return STRATUM_ERR_LIMIT;
   void (*kern)(const GeneralAttention) = nullptr;
-  if (cpw <= 1) kern = attention_general_mma_kernel<1>;
-  else if (cpw <= 2) kern = attention_general_mma_kernel<2>;
-  else if (cpw <= 4) kern = attention_general_mma_kernel<4>;
+  if (cpw <= 1) kern = attention_general_mma_kernel<1, 1>;
+  else if (cpw <= 2) kern = attention_general_mma_kernel<2, 1>;
+  else if (cpw <= 4) kern = attention_general_mma_kernel<4, 1>;
   else return STRATUM_ERR_LIMIT;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -369,7 +434,8 @@ STRATUM_EXPORT int stratum_attention_general_mma(const GeneralAttention* params,
   int st = launch_status();
   if (st || direct) return st;
   const long long rows = (long long)P.n_tokens * P.n_heads;
-  if (P.maps == 1) attention_general_finish_kernel<1><<<(unsigned)((rows + 3) / 4), 128, 0, stream>>>(P);
-  else attention_general_finish_kernel<2><<<(unsigned)((rows + 3) / 4), 128, 0, stream>>>(P);
+  if (rows > 0x7fffffffLL) return STRATUM_ERR_LIMIT;
+  if (P.maps == 1) attention_general_finish_kernel<1><<<(unsigned)rows, 128, 0, stream>>>(P);
+  else attention_general_finish_kernel<2><<<(unsigned)rows, 128, 0, stream>>>(P);
   return launch_status();
 }

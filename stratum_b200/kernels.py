@@ -658,13 +658,20 @@ def attention_general_mma_ok(shape: AttentionShape, q: torch.Tensor, out: torch.
             and out.data_ptr() % 16 == 0 and page_tokens == 64)
 
 
+def attention_general_mma_row_groups(v_dim: int) -> int:
+    """Groups of 16 query rows a CTA of the tensor-core general attention takes in prompt steps."""
+    return int(build.load("attention_general_mma").stratum_attention_general_mma_row_groups(int(v_dim)))
+
+
 def attention_general_mma(shape: AttentionShape, q: torch.Tensor, k_cache: torch.Tensor,
                           v_cache: Optional[torch.Tensor], token_pos: torch.Tensor, token_seq: torch.Tensor,
                           block_table: torch.Tensor, out: torch.Tensor, page_tokens: int, qblocks,
                           tokens_per_block: int, n_splits: int, chunk: int, part_o: Optional[torch.Tensor],
-                          part_ml: Optional[torch.Tensor]) -> None:
+                          part_ml: Optional[torch.Tensor], row_groups: int = 1) -> None:
     """The general attention in bfloat16 on tensor cores.  qblocks: None (one token per sequence, block i is row i)
-    or (seq, first row, tokens) int32 tensors with tokens <= tokens_per_block = 16 // min(group, 16).  The keys
+    or (seq, first row, tokens) int32 tensors with tokens <= row_groups * tokens_per_block, where
+    tokens_per_block = 16 // min(group, 16) tokens make one group of 16 rows and row_groups is 1 or
+    attention_general_mma_row_groups(v_dim) (a CTA then takes that many groups through every tile of keys).  The keys
     of a sequence are cut into n_splits ranges of `chunk` keys (a multiple of 64).  With more than one range or
     more than one map the items' results go through scratch: part_o float32 [tokens*heads*maps*n_splits*v_dim],
     part_ml float32 [tokens*heads*maps*n_splits*2]."""
@@ -674,7 +681,7 @@ def attention_general_mma(shape: AttentionShape, q: torch.Tensor, k_cache: torch
     else:
         qs, qt, qn = qblocks
         p.qb_seq, p.qb_tok0, p.qb_ntok, p.n_qblocks = qs.data_ptr(), qt.data_ptr(), qn.data_ptr(), qs.numel()
-    p.tokens_per_block, p.n_splits, p.chunk = tokens_per_block, n_splits, chunk
+    p.tokens_per_block, p.n_splits, p.chunk, p.reserved = tokens_per_block, n_splits, chunk, row_groups
     through_scratch = n_splits > 1 or shape.maps > 1
     if through_scratch:
         need = q.shape[0] * shape.n_heads * shape.maps * n_splits

@@ -109,11 +109,14 @@ def run_general(att, shape, q: torch.Tensor, cache, step, out: torch.Tensor) -> 
     rows_per_token = min(shape.group, 16)
     per_block = 16 // rows_per_token
     streams = (shape.n_heads // shape.group) * ((shape.group + 15) // 16) * shape.maps
+    row_groups = 1
     if step.all_single:
         qblocks = None
         n_splits, chunk = plan_general_splits(step.n_tokens * streams, step.max_len)
     else:
-        qblocks = step.query_blocks(per_block)
+        # prompts: a CTA takes several groups of 16 rows through every tile of keys, which then comes from L2 once
+        row_groups = K.attention_general_mma_row_groups(shape.v_dim)
+        qblocks = step.query_blocks(per_block * row_groups)
         n_splits, chunk = 1, ((step.max_len + PAGE_TOKENS - 1) // PAGE_TOKENS) * PAGE_TOKENS
     part_o = part_ml = None
     if n_splits > 1 or shape.maps > 1:
@@ -121,4 +124,4 @@ def run_general(att, shape, q: torch.Tensor, cache, step, out: torch.Tensor) -> 
         part_o = att.runtime.scratch("general_attention_part_o", n * shape.v_dim, torch.float32)
         part_ml = att.runtime.scratch("general_attention_part_ml", n * 2, torch.float32)
     K.attention_general_mma(shape, q, cache.k, cache.v, step.token_pos, step.token_seq, cache.block_table, out,
-                            PAGE_TOKENS, qblocks, per_block, n_splits, chunk, part_o, part_ml)
+                            PAGE_TOKENS, qblocks, per_block, n_splits, chunk, part_o, part_ml, row_groups)

@@ -317,6 +317,8 @@ def _fill_cache(rng, seq_lens, n_k, D, n_v, Dv, v_in_k):
     dict(H=4, group=4, maps=2, D=48, Dv=96, v_in_k=False, new=(1, 1, 1, 1), before=(5, 64, 127, 900)),
     dict(H=6, group=2, maps=2, D=16, Dv=24, v_in_k=False, new=(33, 1, 130), before=(0, 77, 64)),
     dict(H=8, group=8, maps=1, D=40, Dv=40, v_in_k=True, new=(150,), before=(0,), window=37),
+    dict(H=16, group=16, maps=1, D=320, Dv=288, v_in_k=True, new=(9, 140), before=(100, 3)),
+    dict(H=3, group=1, maps=2, D=24, Dv=136, v_in_k=False, new=(77, 2, 64), before=(0, 200, 1)),
 ])
 def test_tensor_core_attention_against_cuda_cores(case):
     """The same bfloat16 queries and cache through both kernels: decode steps with the keys cut into ranges,
@@ -344,13 +346,14 @@ def test_tensor_core_attention_against_cuda_cores(case):
     K.attention_general(shape, q, kc, vc, i32(pos), i32(seq), table, ref, 64)
     per_block = 16 // min(group, 16)
     single = all(n == 1 for n in new)
+    groups = 1 if single else K.attention_general_mma_row_groups(Dv)
     for n_splits, chunk in ([(1, 2048), (3, 384), (16, 128)] if single else [(1, 2048)]):
         qblocks = None
         if not single:
             qs, qt, qn, r = [], [], [], 0
             for i, n in enumerate(new):
-                for b in range(0, n, per_block):
-                    qs.append(i); qt.append(r + b); qn.append(min(per_block, n - b))
+                for b in range(0, n, per_block * groups):
+                    qs.append(i); qt.append(r + b); qn.append(min(per_block * groups, n - b))
                 r += n
             qblocks = (i32(qs), i32(qt), i32(qn))
         n_part = T * H * maps * n_splits
@@ -358,7 +361,7 @@ def test_tensor_core_attention_against_cuda_cores(case):
         part_ml = torch.full((n_part * 2,), float("nan"), dtype=torch.float32, device="cuda")
         out = torch.zeros_like(ref)
         K.attention_general_mma(shape, q, kc, vc, i32(pos), i32(seq), table, out, 64, qblocks, per_block, n_splits,
-                                chunk, part_o, part_ml)
+                                chunk, part_o, part_ml, groups)
         torch.cuda.synchronize()
         a, b = out.float().cpu().numpy()[:, :H * Dv], ref.float().cpu().numpy()[:, :H * Dv]
         assert np.isfinite(a).all()
