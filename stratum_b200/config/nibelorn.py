@@ -154,14 +154,23 @@ class NibelornConfig(ModelConfig):
                 lr.require(of != i, "weights_of names the layer itself")
             layers.append(NibelornLayer(kind, mixer, ff, of))
             r.adopt(lr)
-        # a layer that borrows tensors borrows them from a layer that has its own, of the same shape
+        # a layer that borrows tensors borrows them, directly or through other borrowers, from a layer that has its
+        # own, of the same shape
         for i, layer in enumerate(layers):
             if layer.weights_of is None or layer.weights_of >= len(layers):
                 continue
-            src = layers[layer.weights_of]
-            r.require(src.weights_of is None, f"layers[{i}].weights_of={layer.weights_of} names a layer without tensors")
+            j, seen = layer.weights_of, {i}
+            while j not in seen and j < len(layers) and layers[j].weights_of is not None:
+                seen.add(j)
+                j = layers[j].weights_of
+            if j in seen or j >= len(layers):
+                r.problems.append(f"layers[{i}].weights_of={layer.weights_of} leads to no layer with tensors of its own")
+                continue
+            src = layers[j]
+            if j != layer.weights_of:
+                layers[i] = NibelornLayer(layer.kind, layer.mixer, layer.ff, j)
             r.require((src.kind, src.mixer, src.ff) == (layer.kind, layer.mixer, layer.ff),
-                      f"layers[{i}] differs from layers[{layer.weights_of}], whose tensors it uses")
+                      f"layers[{i}] differs from layers[{j}], whose tensors it uses")
         r.finish()
         return cls(vocab=vocab, width=width, eps=eps, layers=tuple(layers),
                    torch_dtype=raw.get("torch_dtype", "bfloat16"))

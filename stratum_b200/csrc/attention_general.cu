@@ -148,6 +148,7 @@ static int launch_general(const GeneralAttention& P, cudaStream_t stream) {
   else if (vch <= 4) AG_LAUNCH(4);
   else if (vch <= 8) AG_LAUNCH(8);
   else if (vch <= 16) AG_LAUNCH(16);
+  else if (vch <= 32) AG_LAUNCH(32);
   else return STRATUM_ERR_LIMIT;
 #undef AG_LAUNCH
   return launch_status();

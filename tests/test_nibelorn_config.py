@@ -30,12 +30,23 @@ def test_configuration_problems_are_listed_together():
     raw["layers"][0]["mixer"]["heads"] = 5                 # 5 heads on 2 kv heads
     raw["layers"][1]["mixer"]["rot"]["dims"] = 7
     raw["layers"][2]["type"] = "recurrent"
-    raw["layers"][4]["weights_of"] = 3                     # layer 3 has no tensors of its own
+    raw["layers"][4]["weights_of"] = 3                     # layer 3 uses layer 0's, which is another kind of layer
     with pytest.raises(ConfigError) as e:
         _cfg(raw)
     text = str(e.value)
-    for piece in ("width", "kv_heads", "rot.dims", "recurrent", "without tensors"):
+    for piece in ("width", "kv_heads", "rot.dims", "recurrent", "differs from layers[0]"):
         assert piece in text, (piece, text)
+
+
+def test_borrowed_tensors_through_another_borrower():
+    raw = copy.deepcopy(NIB_A)
+    raw["layers"].append(dict(raw["layers"][3], weights_of=3))          # 5 -> 3 -> 0
+    cfg = _cfg(raw)
+    assert cfg.layers[5].weights_of == 0
+    raw["layers"][0]["weights_of"] = 5                                  # a ring: nobody has tensors
+    from stratum_b200.config import ConfigError
+    with pytest.raises(ConfigError, match="no layer with tensors"):
+        _cfg(raw)
 
 
 def test_tensor_names_and_shapes():
