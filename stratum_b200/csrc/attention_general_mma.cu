@@ -31,6 +31,22 @@
 // may be served by L1) see what they wrote
 __device__ __forceinline__ uint4 gm_ldg16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
 
+// the same instruction as mma16816, left to the compiler to schedule among its neighbours (its only effect is its result)
+__device__ __forceinline__ void gm_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// A 16 x 16 block of bfloat16 from shared memory as the A operand of m16n8k16: lane l gives the address of row
+// l % 16, columns 8 (l / 16) .. + 7 of the block.
+__device__ __forceinline__ void gm_ldmatrix4(uint32_t (&a)[4], const void* lane_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
+               : "r"((uint32_t)__cvta_generic_to_shared(lane_row)) : "memory");
+}
+
 __host__ __device__ __forceinline__ int gm_q_stride(int D) {       // bytes per row of Q in shared memory: = 64 mod 128
   int s = ((D * 2 + 15) / 16) * 16;
   while (s % 128 != 64) s += 16;
@@ -152,18 +168,27 @@ attention_general_mma_kernel(const GeneralAttention P) {
       const bool any = kw < g_end && kw + 15 >= k_begin;
       if (any) {
         const unsigned char* qg = q_s + (size_t)rg * 16 * qstride;
-#pragma unroll 4
-        for (int c = 0; c < n_kc; c++) {
-          const int d = 32 * c + 8 * t;
-          const bool d_ok = d < D;
-          const uint4 ka = d_ok ? gm_ldg16(kr + (size_t)g * D + d) : zero4;
-          const uint4 kb = d_ok ? gm_ldg16(kr + (size_t)(g + 8) * D + d) : zero4;
-          const uint4 qa = d_ok ? *reinterpret_cast<const uint4*>(qg + (size_t)g * qstride + 2 * d) : zero4;
-          const uint4 qc = d_ok ? *reinterpret_cast<const uint4*>(qg + (size_t)(g + 8) * qstride + 2 * d) : zero4;
-          mma16816(s[0], qa.x, qc.x, qa.y, qc.y, ka.x, ka.y);
-          mma16816(s[0], qa.z, qc.z, qa.w, qc.w, ka.z, ka.w);
-          mma16816(s[1], qa.x, qc.x, qa.y, qc.y, kb.x, kb.y);
-          mma16816(s[1], qa.z, qc.z, qa.w, qc.w, kb.z, kb.w);
+        for (int c0 = 0; c0 < n_kc; c0 += 4) {          // four chunks' loads in flight together
+          uint4 ka[4], kb[4];
+#pragma unroll
+          for (int u = 0; u < 4; u++) {
+            const int d = 32 * (c0 + u) + 8 * t;
+            const bool d_ok = d < D;
+            ka[u] = d_ok ? gm_ldg16(kr + (size_t)g * D + d) : zero4;
+            kb[u] = d_ok ? gm_ldg16(kr + (size_t)(g + 8) * D + d) : zero4;
+          }
+#pragma unroll
+          for (int u = 0; u < 4; u++) {
+            const int d = 32 * (c0 + u) + 8 * t;
+            if (32 * (c0 + u) >= D) break;
+            const bool d_ok = d < D;
+            const uint4 qa = d_ok ? *reinterpret_cast<const uint4*>(qg + (size_t)g * qstride + 2 * d) : zero4;
+            const uint4 qc = d_ok ? *reinterpret_cast<const uint4*>(qg + (size_t)(g + 8) * qstride + 2 * d) : zero4;
+            gm_mma(s[0], qa.x, qc.x, qa.y, qc.y, ka[u].x, ka[u].y);
+            gm_mma(s[1], qa.x, qc.x, qa.y, qc.y, kb[u].x, kb[u].y);
+            gm_mma(s[0], qa.z, qc.z, qa.w, qc.w, ka[u].z, ka[u].w);
+            gm_mma(s[1], qa.z, qc.z, qa.w, qc.w, kb[u].z, kb[u].w);
+          }
         }
       }
       float bm[2] = {-INFINITY, -INFINITY};
@@ -238,22 +263,19 @@ attention_general_mma_kernel(const GeneralAttention P) {
 #pragma unroll
         for (int kb = 0; kb < GM_TILE / 16; kb++) {
           if (kb >= blocks) break;
-          const int a_at = g * GM_PSTRIDE + 16 * kb + 2 * t;
-          const uint32_t h0 = *reinterpret_cast<const uint32_t*>(p_hi + a_at);
-          const uint32_t h1 = *reinterpret_cast<const uint32_t*>(p_hi + a_at + 8 * GM_PSTRIDE);
-          const uint32_t h2 = *reinterpret_cast<const uint32_t*>(p_hi + a_at + 8);
-          const uint32_t h3 = *reinterpret_cast<const uint32_t*>(p_hi + a_at + 8 * GM_PSTRIDE + 8);
-          const uint32_t l0 = *reinterpret_cast<const uint32_t*>(p_lo + a_at);
-          const uint32_t l1 = *reinterpret_cast<const uint32_t*>(p_lo + a_at + 8 * GM_PSTRIDE);
-          const uint32_t l2 = *reinterpret_cast<const uint32_t*>(p_lo + a_at + 8);
-          const uint32_t l3 = *reinterpret_cast<const uint32_t*>(p_lo + a_at + 8 * GM_PSTRIDE + 8);
+          uint32_t hi[4], lo[4], b0[4], b1[4];
+          const int a_at = (lane & 15) * GM_PSTRIDE + 16 * kb + 8 * (lane >> 4);
+          gm_ldmatrix4(hi, p_hi + a_at);
+          gm_ldmatrix4(lo, p_lo + a_at);
 #pragma unroll
           for (int i = 0; i < 4; i++) {
-            const uint32_t b0 = transpose8x8(reg_of(va[kb], i));
-            const uint32_t b1 = transpose8x8(reg_of(vb[kb], i));
-            mma16816(o[rg][4 * cc + i], h0, h1, h2, h3, b0, b1);
-            mma16816(o[rg][4 * cc + i], l0, l1, l2, l3, b0, b1);
+            b0[i] = transpose8x8(reg_of(va[kb], i));
+            b1[i] = transpose8x8(reg_of(vb[kb], i));
           }
+#pragma unroll
+          for (int i = 0; i < 4; i++) gm_mma(o[rg][4 * cc + i], hi[0], hi[1], hi[2], hi[3], b0[i], b1[i]);
+#pragma unroll
+          for (int i = 0; i < 4; i++) gm_mma(o[rg][4 * cc + i], lo[0], lo[1], lo[2], lo[3], b0[i], b1[i]);
         }
       }
       __syncthreads();                             // the tiles of probabilities and the maxima are written again
