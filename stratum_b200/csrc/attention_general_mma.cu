@@ -2,8 +2,8 @@
 //
 // A CTA of four warps owns one work item: up to RG groups of 16 query rows that share their keys (consecutive new
 // tokens of a sequence x the heads of one key/value group, for one score map) and one contiguous range of that
-// sequence's keys.  Keys are visited in tiles of 64 (one page); the groups take every tile in turn, so that the
-// tile's keys and values come from L2 once and from L1 afterwards.  Per tile and group:
+// sequence's keys.  Keys are visited in tiles of 64 (one page); the groups go through every phase of a tile together
+// and share its key and value fragments.  Per tile:
 //   scores   warp w computes the 16 x 16 block of rows x keys 16w..16w+15: mma.sync.m16n8k16 over the key
 //            dimension, Q fragments from shared memory, K fragments straight from the cache rows (a dot product
 //            may visit the dimension in any order as long as Q and K agree: lane t of a row takes the 8
@@ -62,10 +62,10 @@ attention_general_mma_kernel(const GeneralAttention P) {
   const int D = P.qk_dim, Dv = P.v_dim;
   const int qstride = gm_q_stride(D);
   unsigned char* q_s = gm_smem;                                                  // [RG][16][qstride bytes]
-  bf16* p_hi = reinterpret_cast<bf16*>(gm_smem + RG * 16 * qstride);             // [16][GM_PSTRIDE]
-  bf16* p_lo = p_hi + 16 * GM_PSTRIDE;
-  float* max_s = reinterpret_cast<float*>(p_lo + 16 * GM_PSTRIDE);               // [GM_WARPS][16]
-  float* sum_s = max_s + GM_WARPS * 16;                                          // [GM_WARPS][16]
+  bf16* p_hi = reinterpret_cast<bf16*>(gm_smem + RG * 16 * qstride);             // [RG][16][GM_PSTRIDE]
+  bf16* p_lo = p_hi + RG * 16 * GM_PSTRIDE;
+  float* max_s = reinterpret_cast<float*>(p_lo + RG * 16 * GM_PSTRIDE);          // [RG][GM_WARPS][16]
+  float* sum_s = max_s + RG * GM_WARPS * 16;                                     // [GM_WARPS][16]
 
   const int rows_per_token = P.group < 16 ? P.group : 16;
   const int head_groups = (P.group + 15) / 16;
@@ -155,42 +155,43 @@ attention_general_mma_kernel(const GeneralAttention P) {
     const int kw = key0 + 16 * warp;
     const bf16* kr = (const bf16*)P.k_cache + (size_t)page * k_page + k_head + (size_t)(in_page + 16 * warp) * D;
     const bf16* vr = v_base + (size_t)page * v_page + v_head + (size_t)in_page * v_row;
+    // ---- scores of keys key0 + 16 warp + [0, 16), for every group of rows: the key fragments are loaded once
+    float s[RG][2][4];
 #pragma unroll
-    for (int rg = 0; rg < RG; rg++) {
-      // the last position of this group of rows (the same for every thread of the CTA)
-      const int g_first = first_pos + rg * tpg;
-      if (rg > 0 && (rg * tpg >= ntok || key0 > min(g_first + tpg - 1, last_pos))) continue;
-      const int g_end = min(k_end, min(g_first + tpg - 1, last_pos) + 1);      // keys this group can see end here
-      // ---- scores of keys key0 + 16 warp + [0, 16)
-      float s[2][4];
+    for (int rg = 0; rg < RG; rg++)
 #pragma unroll
-      for (int i = 0; i < 2; i++) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
-      const bool any = kw < g_end && kw + 15 >= k_begin;
-      if (any) {
-        const unsigned char* qg = q_s + (size_t)rg * 16 * qstride;
-        for (int c0 = 0; c0 < n_kc; c0 += 4) {          // four chunks' loads in flight together
-          uint4 ka[4], kb[4];
+      for (int i = 0; i < 2; i++) { s[rg][i][0] = s[rg][i][1] = s[rg][i][2] = s[rg][i][3] = 0.f; }
+    const bool any = kw < k_end && kw + 15 >= k_begin;
+    if (any) {
+      for (int c0 = 0; c0 < n_kc; c0 += 4) {            // four chunks' loads in flight together
+        uint4 ka[4], kb[4];
 #pragma unroll
-          for (int u = 0; u < 4; u++) {
-            const int d = 32 * (c0 + u) + 8 * t;
-            const bool d_ok = d < D;
-            ka[u] = d_ok ? gm_ldg16(kr + (size_t)g * D + d) : zero4;
-            kb[u] = d_ok ? gm_ldg16(kr + (size_t)(g + 8) * D + d) : zero4;
-          }
+        for (int u = 0; u < 4; u++) {
+          const int d = 32 * (c0 + u) + 8 * t;
+          const bool d_ok = d < D;
+          ka[u] = d_ok ? gm_ldg16(kr + (size_t)g * D + d) : zero4;
+          kb[u] = d_ok ? gm_ldg16(kr + (size_t)(g + 8) * D + d) : zero4;
+        }
 #pragma unroll
-          for (int u = 0; u < 4; u++) {
-            const int d = 32 * (c0 + u) + 8 * t;
-            if (32 * (c0 + u) >= D) break;
-            const bool d_ok = d < D;
+        for (int u = 0; u < 4; u++) {
+          const int d = 32 * (c0 + u) + 8 * t;
+          if (32 * (c0 + u) >= D) break;
+          const bool d_ok = d < D;
+#pragma unroll
+          for (int rg = 0; rg < RG; rg++) {
+            const unsigned char* qg = q_s + (size_t)rg * 16 * qstride;
             const uint4 qa = d_ok ? *reinterpret_cast<const uint4*>(qg + (size_t)g * qstride + 2 * d) : zero4;
             const uint4 qc = d_ok ? *reinterpret_cast<const uint4*>(qg + (size_t)(g + 8) * qstride + 2 * d) : zero4;
-            gm_mma(s[0], qa.x, qc.x, qa.y, qc.y, ka[u].x, ka[u].y);
-            gm_mma(s[1], qa.x, qc.x, qa.y, qc.y, kb[u].x, kb[u].y);
-            gm_mma(s[0], qa.z, qc.z, qa.w, qc.w, ka[u].z, ka[u].w);
-            gm_mma(s[1], qa.z, qc.z, qa.w, qc.w, kb[u].z, kb[u].w);
+            gm_mma(s[rg][0], qa.x, qc.x, qa.y, qc.y, ka[u].x, ka[u].y);
+            gm_mma(s[rg][1], qa.x, qc.x, qa.y, qc.y, kb[u].x, kb[u].y);
+            gm_mma(s[rg][0], qa.z, qc.z, qa.w, qc.w, ka[u].z, ka[u].w);
+            gm_mma(s[rg][1], qa.z, qc.z, qa.w, qc.w, kb[u].z, kb[u].w);
           }
         }
       }
+    }
+#pragma unroll
+    for (int rg = 0; rg < RG; rg++) {
       float bm[2] = {-INFINITY, -INFINITY};
 #pragma unroll
       for (int i = 0; i < 2; i++) {
@@ -201,27 +202,31 @@ attention_general_mma_kernel(const GeneralAttention P) {
           const int pos = row_pos[rg][e];
           const int lo = (P.window > 0 && pos - P.window + 1 > 0) ? pos - P.window + 1 : 0;
           const bool ok = any && row_ok[rg][e] && key <= pos && key >= lo && key < k_end && key >= k_begin;
-          float v = s[i][j] * row_factor[rg][e];
+          float v = s[rg][i][j] * row_factor[rg][e];
           if (P.softcap > 0.f) v = P.softcap * tanhf(v / P.softcap);
-          s[i][j] = ok ? v : -INFINITY;
-          bm[e] = fmaxf(bm[e], s[i][j]);
+          s[rg][i][j] = ok ? v : -INFINITY;
+          bm[e] = fmaxf(bm[e], s[rg][i][j]);
         }
       }
 #pragma unroll
       for (int e = 0; e < 2; e++) {
         bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 1));
         bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 2));
-        if (t == 0) max_s[warp * 16 + g + 8 * e] = bm[e];
+        if (t == 0) max_s[(rg * GM_WARPS + warp) * 16 + g + 8 * e] = bm[e];
       }
-      __syncthreads();
-      float corr[2], m_use[2];
+    }
+    __syncthreads();
+    float corr[RG][2];
+#pragma unroll
+    for (int rg = 0; rg < RG; rg++) {
+      float m_use[2];
 #pragma unroll
       for (int e = 0; e < 2; e++) {
-        const int r = g + 8 * e;
+        const int r = rg * GM_WARPS * 16 + g + 8 * e;
         const float tile_max = fmaxf(fmaxf(max_s[r], max_s[16 + r]), fmaxf(max_s[32 + r], max_s[48 + r]));
         const float m_new = fmaxf(m_run[rg][e], tile_max);
         m_use[e] = (m_new == -INFINITY) ? 0.f : m_new;      // a row with no key yet: exponents of -inf give 0
-        corr[e] = expf(m_run[rg][e] - m_use[e]);            // first keys: exp(-inf) = 0
+        corr[rg][e] = expf(m_run[rg][e] - m_use[e]);        // first keys: exp(-inf) = 0
         m_run[rg][e] = m_new;
       }
       float psum[2] = {0.f, 0.f};
@@ -229,57 +234,64 @@ attention_general_mma_kernel(const GeneralAttention P) {
       for (int i = 0; i < 2; i++) {
 #pragma unroll
         for (int e = 0; e < 2; e++) {
-          const float p0 = expf(s[i][2 * e] - m_use[e]), p1 = expf(s[i][2 * e + 1] - m_use[e]);
+          const float p0 = expf(s[rg][i][2 * e] - m_use[e]), p1 = expf(s[rg][i][2 * e + 1] - m_use[e]);
           psum[e] += p0 + p1;
           const __nv_bfloat162 hi = __floats2bfloat162_rn(p0, p1);
           const __nv_bfloat162 lo = __floats2bfloat162_rn(p0 - __bfloat162float(hi.x), p1 - __bfloat162float(hi.y));
-          const int at = (g + 8 * e) * GM_PSTRIDE + 16 * warp + 8 * i + 2 * t;
+          const int at = (rg * 16 + g + 8 * e) * GM_PSTRIDE + 16 * warp + 8 * i + 2 * t;
           *reinterpret_cast<__nv_bfloat162*>(p_hi + at) = hi;
           *reinterpret_cast<__nv_bfloat162*>(p_lo + at) = lo;
         }
       }
 #pragma unroll
-      for (int e = 0; e < 2; e++) l_run[rg][e] = l_run[rg][e] * corr[e] + psum[e];
-      __syncthreads();
-      // ---- values: chunks of 32 dimensions c = warp, warp + 4, ...
+      for (int e = 0; e < 2; e++) l_run[rg][e] = l_run[rg][e] * corr[rg][e] + psum[e];
+    }
+    __syncthreads();
+    // ---- values: chunks of 32 dimensions c = warp, warp + 4, ...; the value fragments are loaded and transposed
+    // once for all groups of rows
+#pragma unroll
+    for (int rg = 0; rg < RG; rg++)
 #pragma unroll
       for (int i = 0; i < CPW * 4; i++) {
-        o[rg][i][0] *= corr[0]; o[rg][i][1] *= corr[0]; o[rg][i][2] *= corr[1]; o[rg][i][3] *= corr[1];
+        o[rg][i][0] *= corr[rg][0]; o[rg][i][1] *= corr[rg][0]; o[rg][i][2] *= corr[rg][1]; o[rg][i][3] *= corr[rg][1];
       }
-      const int blocks = min(GM_TILE, g_end - key0 + 15) / 16;        // blocks of 16 keys that hold a key
+    const int blocks = min(GM_TILE, k_end - key0 + 15) / 16;          // blocks of 16 keys that hold a key
 #pragma unroll
-      for (int cc = 0; cc < CPW; cc++) {
-        const int c = warp + GM_WARPS * cc;
-        const int d = 32 * c + 8 * t;
-        if (c >= n_vc) break;
-        // all of the tile's loads of this chunk first, so that their latencies overlap
-        uint4 va[GM_TILE / 16], vb[GM_TILE / 16];
+    for (int cc = 0; cc < CPW; cc++) {
+      const int c = warp + GM_WARPS * cc;
+      const int d = 32 * c + 8 * t;
+      if (c >= n_vc) break;
+      // all of the tile's loads of this chunk first, so that their latencies overlap
+      uint4 va[GM_TILE / 16], vb[GM_TILE / 16];
 #pragma unroll
-        for (int kb = 0; kb < GM_TILE / 16; kb++) {
-          const bool ok = kb < blocks && d < Dv;
-          va[kb] = ok ? gm_ldg16(vr + (size_t)(16 * kb + g) * v_row + d) : zero4;
-          vb[kb] = ok ? gm_ldg16(vr + (size_t)(16 * kb + 8 + g) * v_row + d) : zero4;
+      for (int kb = 0; kb < GM_TILE / 16; kb++) {
+        const bool ok = kb < blocks && d < Dv;
+        va[kb] = ok ? gm_ldg16(vr + (size_t)(16 * kb + g) * v_row + d) : zero4;
+        vb[kb] = ok ? gm_ldg16(vr + (size_t)(16 * kb + 8 + g) * v_row + d) : zero4;
+      }
+#pragma unroll
+      for (int kb = 0; kb < GM_TILE / 16; kb++) {
+        if (kb >= blocks) break;
+        uint32_t b0[4], b1[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          b0[i] = transpose8x8(reg_of(va[kb], i));
+          b1[i] = transpose8x8(reg_of(vb[kb], i));
         }
 #pragma unroll
-        for (int kb = 0; kb < GM_TILE / 16; kb++) {
-          if (kb >= blocks) break;
-          uint32_t hi[4], lo[4], b0[4], b1[4];
-          const int a_at = (lane & 15) * GM_PSTRIDE + 16 * kb + 8 * (lane >> 4);
+        for (int rg = 0; rg < RG; rg++) {
+          uint32_t hi[4], lo[4];
+          const int a_at = (rg * 16 + (lane & 15)) * GM_PSTRIDE + 16 * kb + 8 * (lane >> 4);
           gm_ldmatrix4(hi, p_hi + a_at);
           gm_ldmatrix4(lo, p_lo + a_at);
-#pragma unroll
-          for (int i = 0; i < 4; i++) {
-            b0[i] = transpose8x8(reg_of(va[kb], i));
-            b1[i] = transpose8x8(reg_of(vb[kb], i));
-          }
 #pragma unroll
           for (int i = 0; i < 4; i++) gm_mma(o[rg][4 * cc + i], hi[0], hi[1], hi[2], hi[3], b0[i], b1[i]);
 #pragma unroll
           for (int i = 0; i < 4; i++) gm_mma(o[rg][4 * cc + i], lo[0], lo[1], lo[2], lo[3], b0[i], b1[i]);
         }
       }
-      __syncthreads();                             // the tiles of probabilities and the maxima are written again
     }
+    __syncthreads();                               // the tiles of probabilities and the maxima are written again
   }
 
   const bool direct = P.n_splits == 1 && P.combine == 0;
@@ -405,16 +417,24 @@ __global__ void __launch_bounds__(128) attention_general_finish_kernel(const Gen
 }
 
 STRATUM_EXPORT long long stratum_attention_general_mma_smem(int qk_dim, int row_groups) {
-  return 16LL * row_groups * gm_q_stride(qk_dim) + 2LL * 16 * GM_PSTRIDE * sizeof(bf16) + 2LL * GM_WARPS * 16 * sizeof(float);
+  return 16LL * row_groups * gm_q_stride(qk_dim) + 2LL * row_groups * 16 * GM_PSTRIDE * sizeof(bf16) +
+         (row_groups + 1LL) * GM_WARPS * 16 * sizeof(float);
 }
 
-// Groups of 16 rows a CTA takes for a value size (prompts): what the host cuts its query blocks by.
+// Groups of 16 rows a CTA takes for a value size (prompts): what the host cuts its query blocks by.  Two groups share
+// every key and value fragment (and its transposition) of a tile.  Measured on prompts of 2,048 tokens, four layers:
+// values of 512 (keys of 576) 5.02 ms with two groups against 5.38 with one; values of 256 (keys of 288) 1.83
+// against 1.75.  So: two where a warp holds four chunks of values, else one.  STRATUM_GENERAL_ATTENTION_ROW_GROUPS=1|2
+// forces either (measurements).
 STRATUM_EXPORT int stratum_attention_general_mma_row_groups(int v_dim) {
-  // Measured on 2,048-token prompts with 4 (2 for values of more than 256) groups: 2.96 against 1.74 ms over four
-  // layers of a 2,048-wide model, 8.1 against 5.9 ms of a 4,096-wide one.  The accumulators of several groups
-  // cost more in CTAs per SM than the tiles' second and third readings, which L2 serves, cost in time.  So: one.
-  (void)v_dim;
-  return 1;
+  static int forced = -1;
+  if (forced < 0) {
+    const char* e = getenv("STRATUM_GENERAL_ATTENTION_ROW_GROUPS");
+    forced = e ? atoi(e) : 0;
+  }
+  if (forced == 1 || forced == 2) return forced;
+  const int cpw = ((v_dim + 31) / 32 + GM_WARPS - 1) / GM_WARPS;
+  return cpw > 2 ? 2 : 1;
 }
 
 // q, the caches and out bfloat16.  `reserved` in the parameters: groups of 16 rows per query block (0 or 1: one;
@@ -437,16 +457,16 @@ STRATUM_EXPORT int stratum_attention_general_mma(const GeneralAttention* params,
   const int cpw = (n_vc + GM_WARPS - 1) / GM_WARPS;
   // groups of 16 rows per CTA: as many as the accumulators leave registers for (prompts; decode steps have one)
   const int rg = P.reserved <= 1 ? 1 : P.reserved;
-  if (rg != 1) return STRATUM_ERR_SHAPE;          // the kernel is written for RG groups; only RG = 1 is built (see above)
+  if (rg > 2) return STRATUM_ERR_SHAPE;
   const size_t smem = (size_t)stratum_attention_general_mma_smem(P.qk_dim, rg);
   if (smem > 200 * 1024) return STRATUM_ERR_LIMIT;
   const int head_groups = (P.group + 15) / 16;
   const long long items = (long long)P.n_qblocks * (P.n_heads / P.group) * head_groups * P.maps * P.n_splits;
   if (items > 0x7fffffffLL) return STRATUM_ERR_LIMIT;
   void (*kern)(const GeneralAttention) = nullptr;
-  if (cpw <= 1) kern = attention_general_mma_kernel<1, 1>;
-  else if (cpw <= 2) kern = attention_general_mma_kernel<2, 1>;
-  else if (cpw <= 4) kern = attention_general_mma_kernel<4, 1>;
+  if (cpw <= 1) kern = rg == 1 ? attention_general_mma_kernel<1, 1> : attention_general_mma_kernel<1, 2>;
+  else if (cpw <= 2) kern = rg == 1 ? attention_general_mma_kernel<2, 1> : attention_general_mma_kernel<2, 2>;
+  else if (cpw <= 4) kern = rg == 1 ? attention_general_mma_kernel<4, 1> : attention_general_mma_kernel<4, 2>;
   else return STRATUM_ERR_LIMIT;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

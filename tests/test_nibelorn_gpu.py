@@ -346,8 +346,9 @@ def test_tensor_core_attention_against_cuda_cores(case):
     K.attention_general(shape, q, kc, vc, i32(pos), i32(seq), table, ref, 64)
     per_block = 16 // min(group, 16)
     single = all(n == 1 for n in new)
-    groups = 1 if single else K.attention_general_mma_row_groups(Dv)
-    for n_splits, chunk in ([(1, 2048), (3, 384), (16, 128)] if single else [(1, 2048)]):
+    assert K.attention_general_mma_row_groups(Dv) in (1, 2)
+    # decode steps: one group of 16 rows, the keys in one, three or sixteen ranges; prompts: one and two groups
+    for n_splits, chunk, groups in ([(1, 2048, 1), (3, 384, 1), (16, 128, 1)] if single else [(1, 2048, 1), (1, 2048, 2)]):
         qblocks = None
         if not single:
             qs, qt, qn, r = [], [], [], 0
@@ -413,3 +414,63 @@ def test_per_head_products(rows, heads, n, k, x_step, o_step):
         assert np.max(np.abs(got[:, j * o_step: j * o_step + n] - ref)) <= 2 ** -8 * max(1.0, np.max(np.abs(ref)))
     if o_step > n:                                         # columns between the heads' results are left alone
         assert np.all(got[:, n:o_step] == 7.0)
+
+
+# ------------------------------------------------------------------------------------------ the programs
+def test_command_line_and_trace_replay_program(tmp_path):
+    """`./stratum` on a Nibelorn folder (random weights written by the command line itself from a config file), and
+    `bin/trace_run` fed steps on standard input: a batch of two requests, then single tokens, one request ending
+    earlier, then a request that takes the pages given back."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(CONFIGS["A"]))
+    folder = str(tmp_path / "written")
+    prompt = [3, 1, 4, 1, 5, 9, 2, 6]
+    r = subprocess.run([sys.executable, os.path.join(root, "stratum"), folder, "4", *map(str, prompt), "--fp32",
+                        "--random-weights", "3", "--config", str(cfg_file)], capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr
+    assert "architecture: Nibelorn" in r.stderr
+    from helpers import load_plain
+    cfg, w = load_plain(folder)
+    seq = list(prompt)
+    for _ in range(5):
+        seq.append(int(np.argmax(plain_logits(cfg, w, seq)[-1])))
+    assert r.stdout.split() == [str(t) for t in seq[len(prompt):]]
+
+    path, cfg, w = make(str(tmp_path / "lively"), "A", "float32", seed=21)
+    rng = np.random.default_rng(8)
+    V = cfg["vocab"]
+    a, b, c = (rand_tokens(rng, n, V) for n in (70, 9, 33))
+    ra, rb, rc = (plain_logits(cfg, w, t) for t in (a, b, c))
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:60], "want": [0, 59]},
+                                     {"id": "b", "tokens": b[:5], "want": []}], "end": []}]
+    for i in range(10):
+        ents = [{"id": "a", "tokens": [a[60 + i]], "want": [0]}]
+        end = ["a"] if i == 9 else []
+        if i < 4:
+            ents.append({"id": "b", "tokens": [b[5 + i]], "want": [0]})
+            if i == 3:
+                end.append("b")
+        steps.append({"step": 1 + i, "entries": ents, "end": end})
+    steps.append({"step": 11, "entries": [{"id": "c", "tokens": c, "want": list(range(33))}], "end": ["c"]})
+    out = str(tmp_path / "out")
+    p = subprocess.Popen([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", path, "--dtype", "float32",
+                          "--out", out, "--max-tokens", "192"], stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+    for s in steps:
+        p.stdin.write(json.dumps(s) + "\n")
+        p.stdin.flush()
+        assert p.stdout.readline().strip() == f"done {s['step']}"
+    p.stdin.close()
+    assert p.wait(timeout=600) == 0
+    read = lambda n: np.fromfile(os.path.join(out, f"{n}.f32"), dtype="<f4").reshape(-1, V)   # noqa: E731
+    assert_close(read(0), ra[[0, 59]], "float32", "trace step 0")
+    for i in range(10):
+        got = read(1 + i)
+        assert_close(got[0], ra[60 + i], "float32", f"trace a {i}")
+        if i < 4:
+            assert_close(got[1], rb[5 + i], "float32", f"trace b {i}")
+    assert_close(read(11), rc, "float32", "trace c")
