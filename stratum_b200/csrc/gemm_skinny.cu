@@ -212,8 +212,8 @@ static int launch_skinny(const bf16* x, const bf16* w, const float* bias, void* 
 // x: bf16 [M][ldx], w: bf16 [N][K], bias float32 [N] or null, out [M][ldo] (for SwiGLU: [M][N/2]).
 // Needs K % 8 == 0, ldx % 8 == 0 and 16-byte aligned x and w (checked); M <= 32.
 // act (epilogue 0 only): an activation applied to what is stored, see common.cuh.
-STRATUM_EXPORT int stratum_gemm_skinny_act(const void* x, const void* w, const float* bias, void* out, int epilogue,
-                                           int M, int N, int K, int ldx, int ldo, int act, cudaStream_t stream) {
+STRATUM_EXPORT int stratum_gemm_skinny(const void* x, const void* w, const float* bias, void* out, int epilogue,
+                                       int M, int N, int K, int ldx, int ldo, int act, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (act != 0 && epilogue != 0) return STRATUM_ERR_SHAPE;
   if (M > 32) return STRATUM_ERR_LIMIT;
@@ -230,9 +230,4 @@ STRATUM_EXPORT int stratum_gemm_skinny_act(const void* x, const void* w, const f
                               : launch_skinny<2, 2>(xb, wb, bias, out, epilogue, M, N, K, ldx, ldo, act, stream);
   return small_n ? launch_skinny<4, 1>(xb, wb, bias, out, epilogue, M, N, K, ldx, ldo, act, stream)
                  : launch_skinny<4, 2>(xb, wb, bias, out, epilogue, M, N, K, ldx, ldo, act, stream);
-}
-
-STRATUM_EXPORT int stratum_gemm_skinny(const void* x, const void* w, const float* bias, void* out, int epilogue,
-                                       int M, int N, int K, int ldx, int ldo, cudaStream_t stream) {
-  return stratum_gemm_skinny_act(x, w, bias, out, epilogue, M, N, K, ldx, ldo, 0, stream);
 }

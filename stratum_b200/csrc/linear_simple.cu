@@ -101,9 +101,9 @@ static int launch_linear_simple(const void* x, const void* w, const float* bias,
 
 // x: [M][ldx] T (first K columns used); w: [N][K] T; bias: float32 [N] or null; out: [M][ldo].
 // act (epilogue 0 only): an activation applied to what is stored, see common.cuh.
-STRATUM_EXPORT int stratum_linear_simple_act(const void* x, const void* w, const float* bias, void* out, int dtype,
-                                             int epilogue, int M, int N, int K, int ldx, int ldo, int act,
-                                             cudaStream_t stream) {
+STRATUM_EXPORT int stratum_linear_simple(const void* x, const void* w, const float* bias, void* out, int dtype,
+                                         int epilogue, int M, int N, int K, int ldx, int ldo, int act,
+                                         cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || ldx < K || ldo < N) return STRATUM_ERR_SHAPE;
   if (act != 0 && epilogue != 0) return STRATUM_ERR_SHAPE;
@@ -113,12 +113,6 @@ STRATUM_EXPORT int stratum_linear_simple_act(const void* x, const void* w, const
   if (dtype == STRATUM_DT_BF16)
     return launch_linear_simple<bf16>(x, w, bias, out, epilogue, M, N, K, ldx, ldo, stream, 1, 0, 0, 0, act);
   return STRATUM_ERR_DTYPE;
-}
-
-STRATUM_EXPORT int stratum_linear_simple(const void* x, const void* w, const float* bias, void* out, int dtype,
-                                         int epilogue, int M, int N, int K, int ldx, int ldo,
-                                         cudaStream_t stream) {
-  return stratum_linear_simple_act(x, w, bias, out, dtype, epilogue, M, N, K, ldx, ldo, 0, stream);
 }
 
 // The same product once per head: head j multiplies columns [j * x_step, j * x_step + K) of x by the matrix

@@ -290,7 +290,7 @@ def linear_simple(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
     want = x.dtype if epilogue == EPI_STORE else torch.float32
     if out.dtype != want:
         raise KernelError(f"linear: epilogue {epilogue} writes {want}, out is {out.dtype}")
-    f = _fn("linear_simple", "stratum_linear_simple_act",
+    f = _fn("linear_simple", "stratum_linear_simple",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
              c_void_p])
     _check(f(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), dtype_code(x.dtype), epilogue, M, N, K, x.stride(0),
@@ -353,7 +353,7 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
     """bfloat16, at most 32 rows of x: the weight-streaming tensor-core kernel (see EPI_*; act as linear_simple's)."""
     M, N, Kd = _linear_shapes(x, w, bias, out, epilogue, "gemm_skinny")
     _need(x, "x", torch.bfloat16, contiguous=False)
-    f = _fn("gemm_skinny", "stratum_gemm_skinny_act",
+    f = _fn("gemm_skinny", "stratum_gemm_skinny",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
     _check(f(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), epilogue, M, N, Kd, x.stride(0), out.stride(0), act,
              _stream()), "gemm_skinny")
