@@ -182,7 +182,8 @@ STRATUM_EXPORT int stratum_rmsnorm_heads(void* x, int dtype, int n_rows, int str
 }
 
 // ---------------------------------------------------------------- Dynamic Tanh
-// y = tanh(alpha * x) * w + b: a norm without mean or variance; alpha is one learned number, read from the
+// y = tanh(alpha * x) * w + b: an elementwise squashing that stands where a norm would: no row statistic is
+// taken; alpha is one learned number, read from the
 // device.  x float32 [*, hidden]; row r of the output reads row rows[r] of x when rows != nullptr.
 template <typename T>
 __global__ void dynamic_tanh_kernel(const float* __restrict__ x, const float* __restrict__ alpha,

@@ -1,6 +1,6 @@
 """Norms on the residual stream.
 RMSNorm: y = x / sqrt(mean(x^2) + eps) * gain  (stratum/native/stratum_arch_llama.inc.c:45-76).
-Dynamic Tanh: y = tanh(alpha x) * w + b, which computes no mean and no variance."""
+Dynamic Tanh: y = tanh(alpha x) * w + b, elementwise: it stands where a norm would and takes no row statistic."""
 from __future__ import annotations
 
 from typing import Dict, Mapping, Optional

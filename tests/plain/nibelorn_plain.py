@@ -4,7 +4,7 @@ Whole sequences, no cache, one function per mechanism, float64 throughout, no co
 the product package.  Notation: h is a mixer's input [T, width]; p the positions 0..T-1; a
 weight matrix is [out, in] and acts as h @ W.T.
 
-  dynamic tanh        y = tanh(alpha x) * w + b                     (no mean, no variance)
+  dynamic tanh        y = tanh(alpha x) * w + b                     (elementwise; no row statistic)
   rotation            pairs (i, i + n/2), i < n/2, angle p * base^(-2i/n):
                       (u, v) -> (u cos - v sin, v cos + u sin)
   latent attention    q = Wq h split per head into [d plain | r rotated];  Wdkv h = [c' | kr];

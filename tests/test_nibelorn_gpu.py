@@ -311,10 +311,10 @@ def _fill_cache(rng, seq_lens, n_k, D, n_v, Dv, v_in_k):
 
 @pytest.mark.parametrize("case", [
     # heads, group, maps, D, Dv, v_in_k, new tokens per sequence, cached before
-    dict(H=4, group=4, maps=1, D=144, Dv=128, v_in_k=True, new=(1, 1, 1), before=(0, 63, 700)),
+    dict(H=5, group=5, maps=1, D=136, Dv=120, v_in_k=True, new=(1, 1, 1), before=(0, 63, 700)),
     dict(H=16, group=16, maps=1, D=576, Dv=512, v_in_k=True, new=(1, 1), before=(300, 1100)),
     dict(H=20, group=20, maps=1, D=72, Dv=64, v_in_k=True, new=(5, 70), before=(0, 130)),
-    dict(H=4, group=4, maps=2, D=48, Dv=96, v_in_k=False, new=(1, 1, 1, 1), before=(5, 64, 127, 900)),
+    dict(H=6, group=3, maps=2, D=56, Dv=88, v_in_k=False, new=(1, 1, 1, 1), before=(5, 64, 127, 900)),
     dict(H=6, group=2, maps=2, D=16, Dv=24, v_in_k=False, new=(33, 1, 130), before=(0, 77, 64)),
     dict(H=8, group=8, maps=1, D=40, Dv=40, v_in_k=True, new=(150,), before=(0,), window=37),
     dict(H=16, group=16, maps=1, D=320, Dv=288, v_in_k=True, new=(9, 140), before=(100, 3)),
