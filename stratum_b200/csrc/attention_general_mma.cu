@@ -190,6 +190,9 @@ attention_general_mma_kernel(const GeneralAttention P) {
         }
       }
     }
+    // a tile every row of the CTA sees whole (all of it at or before the first row's position, inside the item's
+    // range, no window) needs no mask: rows that do not exist carry zeros and are never written
+    const bool whole_tile = P.window == 0 && key0 + GM_TILE - 1 <= first_pos && key0 >= k_begin && key0 + GM_TILE <= k_end;
 #pragma unroll
     for (int rg = 0; rg < RG; rg++) {
       float bm[2] = {-INFINITY, -INFINITY};
@@ -198,14 +201,17 @@ attention_general_mma_kernel(const GeneralAttention P) {
 #pragma unroll
         for (int j = 0; j < 4; j++) {
           const int e = j >> 1;
-          const int key = kw + 8 * i + 2 * t + (j & 1);
-          const int pos = row_pos[rg][e];
-          const int lo = (P.window > 0 && pos - P.window + 1 > 0) ? pos - P.window + 1 : 0;
-          const bool ok = any && row_ok[rg][e] && key <= pos && key >= lo && key < k_end && key >= k_begin;
           float v = s[rg][i][j] * row_factor[rg][e];
           if (P.softcap > 0.f) v = P.softcap * tanhf(v / P.softcap);
-          s[rg][i][j] = ok ? v : -INFINITY;
-          bm[e] = fmaxf(bm[e], s[rg][i][j]);
+          if (!whole_tile) {
+            const int key = kw + 8 * i + 2 * t + (j & 1);
+            const int pos = row_pos[rg][e];
+            const int lo = (P.window > 0 && pos - P.window + 1 > 0) ? pos - P.window + 1 : 0;
+            const bool ok = any && row_ok[rg][e] && key <= pos && key >= lo && key < k_end && key >= k_begin;
+            v = ok ? v : -INFINITY;
+          }
+          s[rg][i][j] = v;
+          bm[e] = fmaxf(bm[e], v);
         }
       }
 #pragma unroll
@@ -226,7 +232,7 @@ attention_general_mma_kernel(const GeneralAttention P) {
         const float tile_max = fmaxf(fmaxf(max_s[r], max_s[16 + r]), fmaxf(max_s[32 + r], max_s[48 + r]));
         const float m_new = fmaxf(m_run[rg][e], tile_max);
         m_use[e] = (m_new == -INFINITY) ? 0.f : m_new;      // a row with no key yet: exponents of -inf give 0
-        corr[rg][e] = expf(m_run[rg][e] - m_use[e]);        // first keys: exp(-inf) = 0
+        corr[rg][e] = __expf(m_run[rg][e] - m_use[e]);      // first keys: exp(-inf) = 0
         m_run[rg][e] = m_new;
       }
       float psum[2] = {0.f, 0.f};
@@ -234,7 +240,7 @@ attention_general_mma_kernel(const GeneralAttention P) {
       for (int i = 0; i < 2; i++) {
 #pragma unroll
         for (int e = 0; e < 2; e++) {
-          const float p0 = expf(s[rg][i][2 * e] - m_use[e]), p1 = expf(s[rg][i][2 * e + 1] - m_use[e]);
+          const float p0 = __expf(s[rg][i][2 * e] - m_use[e]), p1 = __expf(s[rg][i][2 * e + 1] - m_use[e]);
           psum[e] += p0 + p1;
           const __nv_bfloat162 hi = __floats2bfloat162_rn(p0, p1);
           const __nv_bfloat162 lo = __floats2bfloat162_rn(p0 - __bfloat162float(hi.x), p1 - __bfloat162float(hi.y));
