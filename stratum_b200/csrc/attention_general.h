@@ -16,11 +16,13 @@ struct GeneralAttention {
   const int* qb_ntok;
   float* part_o;            // scratch of the key splits (tensor-core decode kernel)
   float* part_ml;
+  const int* seq_start;     // dense keys (tensor-core kernel): first row of every sequence of the step
   int ldq, ldo, bt_stride, n_tokens;
   int n_heads, group, maps;
   int qk_dim, v_dim, n_k_heads, n_v_heads, v_in_k;
   int page_tokens, window, combine, gate_col;
   int temp_every, n_qblocks, tokens_per_block, n_splits, chunk, reserved;
+  int dense, ldk, ldv, reserved2;   // dense: keys and values are rows of plain matrices (see attention_general_mma.cu)
   float scale, softcap, temp_coef, lambda, out_scale, eps;
 };
 

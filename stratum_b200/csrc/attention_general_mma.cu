@@ -14,6 +14,9 @@
 //            bfloat16 part (p = hi + lo to 16 bits of mantissa) that go through shared memory, and warp w adds
 //            hi V + lo V for the chunks of 32 value dimensions c = w, w + 4, ...  (V fragments straight from the
 //            cache rows, transposed by movmatrix as in attention_mma.cu).
+// Keys and values come from the paged cache, or (`dense`) from two plain matrices that hold, from row seq_start[s]
+// on, the keys and values of sequence s by position (a mixer that forms its heads' keys and values for a whole
+// prompt; the matrices have 64 readable rows beyond the last sequence's).
 // With one key range and one map the normalised result is written directly.  Otherwise every item leaves its
 // unnormalised value sum, its maximum and its denominator in scratch, and the finishing kernel merges the
 // ranges in order and combines the maps (see attention_general.cu for the formulas).
@@ -109,7 +112,9 @@ attention_general_mma_kernel(const GeneralAttention P) {
   int k_begin = split * P.chunk;
   const int k_end = min((split + 1) * P.chunk, last_pos + 1);
   if (k_begin < (lo_block / GM_TILE) * GM_TILE) k_begin = (lo_block / GM_TILE) * GM_TILE;
-  const int* bt = P.block_table + (size_t)seq * P.bt_stride;
+  const bool dense = P.dense != 0;
+  const int* bt = dense ? nullptr : P.block_table + (size_t)seq * P.bt_stride;
+  const size_t seq_row0 = dense ? (size_t)P.seq_start[seq] : 0;
 
   // Q rows of this item into shared memory (16 bytes per thread and turn; rows that do not exist are zero)
   {
@@ -132,7 +137,8 @@ attention_general_mma_kernel(const GeneralAttention P) {
   const size_t k_page = (size_t)P.n_k_heads * P.page_tokens * D;
   const size_t k_head = (size_t)(kv * P.maps + map) * P.page_tokens * D;
   const bf16* v_base = P.v_in_k ? (const bf16*)P.k_cache : (const bf16*)P.v_cache;
-  const int v_row = P.v_in_k ? D : Dv;
+  const int v_row = dense ? P.ldv : (P.v_in_k ? D : Dv);
+  const int k_row = dense ? P.ldk : D;
   const size_t v_page = P.v_in_k ? k_page : (size_t)P.n_v_heads * P.page_tokens * Dv;
   const size_t v_head = P.v_in_k ? (size_t)(kv * P.maps) * P.page_tokens * D : (size_t)kv * P.page_tokens * Dv;
   const int n_kc = (D + 31) / 32;                 // chunks of the key dimension
@@ -150,11 +156,18 @@ attention_general_mma_kernel(const GeneralAttention P) {
   const uint4 zero4 = make_uint4(0, 0, 0, 0);
 
   for (int key0 = (k_begin / GM_TILE) * GM_TILE; key0 < k_end; key0 += GM_TILE) {
-    const int page = bt[key0 / P.page_tokens];
-    const int in_page = key0 % P.page_tokens;
     const int kw = key0 + 16 * warp;
-    const bf16* kr = (const bf16*)P.k_cache + (size_t)page * k_page + k_head + (size_t)(in_page + 16 * warp) * D;
-    const bf16* vr = v_base + (size_t)page * v_page + v_head + (size_t)in_page * v_row;
+    const bf16* kr;
+    const bf16* vr;
+    if (dense) {                                   // key j of the sequence is row seq_row0 + j of the matrices
+      kr = (const bf16*)P.k_cache + (seq_row0 + kw) * k_row + (size_t)(kv * P.maps + map) * D;
+      vr = (const bf16*)P.v_cache + (seq_row0 + key0) * v_row + (size_t)kv * Dv;
+    } else {
+      const int page = bt[key0 / P.page_tokens];
+      const int in_page = key0 % P.page_tokens;
+      kr = (const bf16*)P.k_cache + (size_t)page * k_page + k_head + (size_t)(in_page + 16 * warp) * D;
+      vr = v_base + (size_t)page * v_page + v_head + (size_t)in_page * v_row;
+    }
     // ---- scores of keys key0 + 16 warp + [0, 16), for every group of rows: the key fragments are loaded once
     float s[RG][2][4];
 #pragma unroll
@@ -169,8 +182,8 @@ attention_general_mma_kernel(const GeneralAttention P) {
         for (int u = 0; u < 4; u++) {
           const int d = 32 * (c0 + u) + 8 * t;
           const bool d_ok = d < D;
-          ka[u] = d_ok ? gm_ldg16(kr + (size_t)g * D + d) : zero4;
-          kb[u] = d_ok ? gm_ldg16(kr + (size_t)(g + 8) * D + d) : zero4;
+          ka[u] = d_ok ? gm_ldg16(kr + (size_t)g * k_row + d) : zero4;
+          kb[u] = d_ok ? gm_ldg16(kr + (size_t)(g + 8) * k_row + d) : zero4;
         }
 #pragma unroll
         for (int u = 0; u < 4; u++) {
@@ -429,9 +442,10 @@ STRATUM_EXPORT long long stratum_attention_general_mma_smem(int qk_dim, int row_
 
 // Groups of 16 rows a CTA takes for a value size (prompts): what the host cuts its query blocks by.  Two groups share
 // every key and value fragment (and its transposition) of a tile.  Measured on prompts of 2,048 tokens, four layers:
-// values of 512 (keys of 576) 5.02 ms with two groups against 5.38 with one; values of 256 (keys of 288) 1.83
-// against 1.75.  So: two where a warp holds four chunks of values, else one.  STRATUM_GENERAL_ATTENTION_ROW_GROUPS=1|2
-// forces either (measurements).
+// values of 512 (keys of 576, four chunks of values a warp) 5.02 ms with two groups against 5.38 with one; values of
+// 256 (keys of 288, two chunks a warp) 1.83 against 1.75; values of 64 to 128 (one chunk a warp: heads of ordinary
+// sizes) 2.36 against 2.41 ms a prompt step and 4.94 against 5.31.  So: one group where a warp holds two chunks,
+// else two.  STRATUM_GENERAL_ATTENTION_ROW_GROUPS=1|2 forces either (measurements).
 STRATUM_EXPORT int stratum_attention_general_mma_row_groups(int v_dim) {
   static int forced = -1;
   if (forced < 0) {
@@ -440,7 +454,7 @@ STRATUM_EXPORT int stratum_attention_general_mma_row_groups(int v_dim) {
   }
   if (forced == 1 || forced == 2) return forced;
   const int cpw = ((v_dim + 31) / 32 + GM_WARPS - 1) / GM_WARPS;
-  return cpw > 2 ? 2 : 1;
+  return cpw == 2 ? 1 : 2;
 }
 
 // q, the caches and out bfloat16.  `reserved` in the parameters: groups of 16 rows per query block (0 or 1: one;
@@ -452,6 +466,9 @@ STRATUM_EXPORT int stratum_attention_general_mma(const GeneralAttention* params,
   if (P.n_tokens <= 0 || P.n_qblocks <= 0) return 0;
   const int bad = general_attention_check(P);
   if (bad) return bad;
+  if (P.dense && (P.v_in_k || !P.seq_start || P.ldk % 8 != 0 || P.ldv % 8 != 0 ||
+                  P.ldk < P.n_k_heads * P.qk_dim || P.ldv < P.n_v_heads * P.v_dim))
+    return STRATUM_ERR_SHAPE;
   if (P.qk_dim % 8 != 0 || P.v_dim % 8 != 0 || P.ldq % 8 != 0 || P.ldo % 8 != 0 || P.page_tokens != GM_TILE)
     return STRATUM_ERR_SHAPE;
   if ((((uintptr_t)P.q | (uintptr_t)P.out | (uintptr_t)P.k_cache | (uintptr_t)P.v_cache) & 15) != 0)

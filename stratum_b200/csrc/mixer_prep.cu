@@ -8,6 +8,7 @@
 //   key head j     the first k_norm_n dimensions become u / sqrt(mean(u^2) + eps) * gain (k_norm_n = 0: as they are),
 //                  the dimensions [k_rot_off, k_rot_off + 2 R) are rotated, and the head goes to the token's row of
 //                  the key cache [pages][n_k][page_tokens][k_dim];
+//                  with k_out the same numbers also go to row t of that matrix (rows of tokens of no sequence: zeros);
 //   value head j   goes to the value cache [pages][n_v][page_tokens][v_dim]  (n_v = 0: the mixer keeps no values).
 // Rotation: pair (i, i + R), i < R, angle a = (float)p * inv_freq[i]:  (u, v) -> (u cos a - v sin a, v cos a + u sin a).
 // Everything is evaluated in float32 and rounded once to the storage type.  One block per token; the order of
@@ -26,6 +27,7 @@ struct MixerPrep {
   void* k_cache;
   void* v_cache;
   void* q_out;
+  void* k_out;
   int ld, bt_stride, n_tokens, rot_pairs;
   int n_q, q_dim, q_col, q_rot_off;
   int n_k, k_dim, k_col, k_rot_off, k_norm_n;
@@ -33,6 +35,7 @@ struct MixerPrep {
   int page_tokens, write_cache;
   float eps;
   int q_out_ld, q_out_step, q_out_off;
+  int k_out_ld, reserved;
 };
 
 template <typename T>
@@ -44,6 +47,10 @@ __global__ void __launch_bounds__(128) mixer_prep_kernel(const MixerPrep P) {
   const int seq = P.token_seq[t];
   if (seq < 0) {                                    // a padding token
     pdl_wait();
+    if (P.k_out) {
+      T* ko = (T*)P.k_out + (size_t)t * P.k_out_ld;
+      for (int d = threadIdx.x; d < P.n_k * P.k_dim; d += blockDim.x) ko[d] = from_float<T>(0.f);
+    }
     return;
   }
   const int pos = P.token_pos[t];
@@ -104,6 +111,7 @@ __global__ void __launch_bounds__(128) mixer_prep_kernel(const MixerPrep P) {
         }
       }
       dst[d] = from_float<T>(v);
+      if (P.k_out) ((T*)P.k_out)[(size_t)t * P.k_out_ld + (size_t)j * P.k_dim + d] = from_float<T>(v);
     }
   }
   for (int it = threadIdx.x; it < P.n_v * P.v_dim; it += blockDim.x) {

@@ -530,12 +530,13 @@ class _MixerPrep(ctypes.Structure):
     """Mirror of struct MixerPrep in csrc/mixer_prep.cu."""
     _fields_ = [("x", c_void_p), ("token_pos", c_void_p), ("token_seq", c_void_p), ("block_table", c_void_p),
                 ("inv_freq", c_void_p), ("k_norm_gain", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p),
-                ("q_out", c_void_p), ("ld", c_int), ("bt_stride", c_int), ("n_tokens", c_int), ("rot_pairs", c_int),
+                ("q_out", c_void_p), ("k_out", c_void_p), ("ld", c_int), ("bt_stride", c_int), ("n_tokens", c_int), ("rot_pairs", c_int),
                 ("n_q", c_int), ("q_dim", c_int), ("q_col", c_int), ("q_rot_off", c_int),
                 ("n_k", c_int), ("k_dim", c_int), ("k_col", c_int), ("k_rot_off", c_int), ("k_norm_n", c_int),
                 ("n_v", c_int), ("v_dim", c_int), ("v_col", c_int),
                 ("page_tokens", c_int), ("write_cache", c_int), ("eps", c_float),
-                ("q_out_ld", c_int), ("q_out_step", c_int), ("q_out_off", c_int)]
+                ("q_out_ld", c_int), ("q_out_step", c_int), ("q_out_off", c_int), ("k_out_ld", c_int),
+                ("reserved", c_int)]
 
 
 def mixer_prep(x: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor, block_table: Optional[torch.Tensor],
@@ -543,13 +544,14 @@ def mixer_prep(x: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor
                *, queries=(0, 0, 0), keys=(0, 0, 0), values=(0, 0, 0), inv_freq: Optional[torch.Tensor] = None,
                q_rot_off: int = 0, k_rot_off: int = 0, k_norm_gain: Optional[torch.Tensor] = None,
                eps: float = 0.0, q_out: Optional[torch.Tensor] = None, q_out_step: int = 0,
-               q_out_off: int = 0) -> None:
+               q_out_off: int = 0, k_out: Optional[torch.Tensor] = None) -> None:
     """Between a fused projection and attention.  x [tokens, ld] holds runs of equal heads: queries, keys, values,
     each given as (heads, head size, first column).  Queries: dimensions [q_rot_off, q_rot_off + 2R) rotated in
     place (R = len(inv_freq), pairs (i, i + R)); with q_out [tokens, *] the dimensions from q_rot_off on go, the
     first 2R rotated, to q_out[:, j * q_out_step + q_out_off ...] for head j instead.  Keys: the first len(k_norm_gain) dimensions divided by their
     root mean square (eps inside the root) times the gain, dimensions [k_rot_off, k_rot_off + 2R) rotated, then
-    appended to k_cache.  Values: appended to v_cache.  Tokens of no sequence are left alone."""
+    appended to k_cache, and with k_out [tokens, *] also written to its row t (zeros for tokens of no sequence).
+    Values: appended to v_cache.  Tokens of no sequence are left alone otherwise."""
     _need(x, "x", contiguous=False); _need(token_pos, "token_pos", torch.int32)
     _need(token_seq, "token_seq", torch.int32)
     p = _MixerPrep()
@@ -569,6 +571,11 @@ def mixer_prep(x: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor
     if q_out is not None:
         _need(q_out, "q_out", x.dtype, contiguous=False)
         p.q_out, p.q_out_ld, p.q_out_step, p.q_out_off = q_out.data_ptr(), q_out.stride(0), q_out_step, q_out_off
+    if k_out is not None:
+        _need(k_out, "k_out", x.dtype, contiguous=False)
+        if not write_cache:
+            raise KernelError("mixer_prep: k_out goes with the cache write")
+        p.k_out, p.k_out_ld = k_out.data_ptr(), k_out.stride(0)
     if write_cache:
         _need(block_table, "block_table", torch.int32, contiguous=False)
         p.block_table, p.bt_stride = block_table.data_ptr(), block_table.stride(0)
@@ -587,13 +594,14 @@ class _GeneralAttention(ctypes.Structure):
     _fields_ = [("q", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p), ("out", c_void_p),
                 ("token_pos", c_void_p), ("token_seq", c_void_p), ("block_table", c_void_p),
                 ("qb_seq", c_void_p), ("qb_tok0", c_void_p), ("qb_ntok", c_void_p),
-                ("part_o", c_void_p), ("part_ml", c_void_p),
+                ("part_o", c_void_p), ("part_ml", c_void_p), ("seq_start", c_void_p),
                 ("ldq", c_int), ("ldo", c_int), ("bt_stride", c_int), ("n_tokens", c_int),
                 ("n_heads", c_int), ("group", c_int), ("maps", c_int),
                 ("qk_dim", c_int), ("v_dim", c_int), ("n_k_heads", c_int), ("n_v_heads", c_int), ("v_in_k", c_int),
                 ("page_tokens", c_int), ("window", c_int), ("combine", c_int), ("gate_col", c_int),
                 ("temp_every", c_int), ("n_qblocks", c_int), ("tokens_per_block", c_int), ("n_splits", c_int),
                 ("chunk", c_int), ("reserved", c_int),
+                ("dense", c_int), ("ldk", c_int), ("ldv", c_int), ("reserved2", c_int),
                 ("scale", c_float), ("softcap", c_float), ("temp_coef", c_float), ("lam", c_float),
                 ("out_scale", c_float), ("eps", c_float)]
 
@@ -623,9 +631,20 @@ class AttentionShape:
 
 
 def _general_params(shape: AttentionShape, q, k_cache, v_cache, token_pos, token_seq, block_table, out,
-                    page_tokens: int) -> "_GeneralAttention":
+                    page_tokens: int, seq_start: Optional[torch.Tensor] = None) -> "_GeneralAttention":
     _need(q, "q", contiguous=False); _need(k_cache, "k_cache", q.dtype); _need(out, "out", q.dtype, contiguous=False)
     _need(token_pos, "token_pos", torch.int32); _need(token_seq, "token_seq", torch.int32)
+    if seq_start is not None:                 # keys and values as plain matrices, rows by sequence and position
+        _need(seq_start, "seq_start", torch.int32); _need(v_cache, "v_cache", q.dtype)
+        if k_cache.dim() != 2 or v_cache.dim() != 2 or shape.v_in_k:
+            raise KernelError("attention_general: dense keys and values are two matrices [rows, heads * size]")
+        p = _GeneralAttention()
+        shape.fill(p)
+        p.q, p.k_cache, p.v_cache, p.out = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr()
+        p.token_pos, p.token_seq, p.seq_start = token_pos.data_ptr(), token_seq.data_ptr(), seq_start.data_ptr()
+        p.dense, p.ldk, p.ldv = 1, k_cache.stride(0), v_cache.stride(0)
+        p.ldq, p.ldo, p.n_tokens, p.page_tokens = q.stride(0), out.stride(0), q.shape[0], page_tokens
+        return p
     _need(block_table, "block_table", torch.int32, contiguous=False)
     if q.stride(-1) != 1 or out.stride(-1) != 1:
         raise KernelError("attention_general: rows must be contiguous")
@@ -667,15 +686,18 @@ def attention_general_mma(shape: AttentionShape, q: torch.Tensor, k_cache: torch
                           v_cache: Optional[torch.Tensor], token_pos: torch.Tensor, token_seq: torch.Tensor,
                           block_table: torch.Tensor, out: torch.Tensor, page_tokens: int, qblocks,
                           tokens_per_block: int, n_splits: int, chunk: int, part_o: Optional[torch.Tensor],
-                          part_ml: Optional[torch.Tensor], row_groups: int = 1) -> None:
+                          part_ml: Optional[torch.Tensor], row_groups: int = 1,
+                          seq_start: Optional[torch.Tensor] = None) -> None:
     """The general attention in bfloat16 on tensor cores.  qblocks: None (one token per sequence, block i is row i)
     or (seq, first row, tokens) int32 tensors with tokens <= row_groups * tokens_per_block, where
     tokens_per_block = 16 // min(group, 16) tokens make one group of 16 rows and row_groups is 1 or
     attention_general_mma_row_groups(v_dim) (a CTA then takes that many groups through every tile of keys).  The keys
     of a sequence are cut into n_splits ranges of `chunk` keys (a multiple of 64).  With more than one range or
     more than one map the items' results go through scratch: part_o float32 [tokens*heads*maps*n_splits*v_dim],
-    part_ml float32 [tokens*heads*maps*n_splits*2]."""
-    p = _general_params(shape, q, k_cache, v_cache, token_pos, token_seq, block_table, out, page_tokens)
+    part_ml float32 [tokens*heads*maps*n_splits*2].  seq_start (int32, the first row of every sequence of the step):
+    k_cache and v_cache are then plain matrices [rows, heads * size] that hold sequence s's keys and values by
+    position from row seq_start[s] on, with 64 readable rows beyond the last sequence's; no block table."""
+    p = _general_params(shape, q, k_cache, v_cache, token_pos, token_seq, block_table, out, page_tokens, seq_start)
     if qblocks is None:
         p.n_qblocks = q.shape[0]
     else:

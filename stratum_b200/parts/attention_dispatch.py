@@ -95,6 +95,19 @@ def plan_general_splits(n_items: int, max_len: int):
     return (max_len + chunk - 1) // chunk, chunk
 
 
+def run_general_dense(att, shape, q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, step,
+                      out: torch.Tensor) -> None:
+    """The tensor-core general attention of a prompt step whose sequences all begin at position 0, over keys and
+    values the mixer formed for the step's tokens: plain matrices, row = packed row of the token (so sequence s's
+    key of position j is row seq_start[s] + j), with 64 readable rows beyond the step's."""
+    per_block = 16 // min(shape.group, 16)
+    row_groups = K.attention_general_mma_row_groups(shape.v_dim)
+    chunk = ((step.max_len + PAGE_TOKENS - 1) // PAGE_TOKENS) * PAGE_TOKENS
+    K.attention_general_mma(shape, q, keys, values, step.token_pos, step.token_seq, None, out, PAGE_TOKENS,
+                            step.query_blocks(per_block * row_groups), per_block, 1, chunk, None, None, row_groups,
+                            seq_start=step.seq_start)
+
+
 def run_general(att, shape, q: torch.Tensor, cache, step, out: torch.Tensor) -> None:
     """Attention of the shapes kernels.AttentionShape describes (key and value sizes of their own, values inside the
     key rows, several maps per head): q [tokens, *] holds head j's map m at column (j * maps + m) * qk_dim.

@@ -474,3 +474,54 @@ def test_command_line_and_trace_replay_program(tmp_path):
         if i < 4:
             assert_close(got[1], rb[5 + i], "float32", f"trace b {i}")
     assert_close(read(11), rc, "float32", "trace c")
+
+
+def test_long_prompts_take_the_per_head_form(setup, monkeypatch):
+    """bfloat16 prompts that begin at position 0 and bring 256 tokens or more form their heads' keys and values
+    (latent attention) instead of attending in the latent space: the same logits, to bfloat16 rounding, as the plain
+    implementation and as the absorbed form; the cache they leave serves the decoded tokens that follow; a portion that
+    continues a sequence takes the absorbed form again."""
+    from stratum_b200 import kernels as K
+    from stratum_b200.engine import StepEntry
+    name, dtype, cfg, w, engine, _ = setup
+    if dtype != "bfloat16" or name == "B":
+        pytest.skip("the per-head form is a bfloat16 form for sizes in multiples of 8")
+    dense_calls = []
+    real = K.attention_general_mma
+
+    def spy(*args, **kw):
+        dense_calls.append(kw.get("seq_start") is not None)
+        return real(*args, **kw)
+    monkeypatch.setattr(K, "attention_general_mma", spy)
+    rng = np.random.default_rng(12)
+    V = cfg["vocab"]
+    prompts = [rand_tokens(rng, n, V) for n in (300, 70, 257)]
+    tails = [rand_tokens(rng, 3, V) for _ in prompts]
+    refs = [plain_logits(cfg, w, p + t) for p, t in zip(prompts, tails)]
+    slots = [engine.acquire() for _ in prompts]
+    out = engine.step([StepEntry(s, p, [0, len(p) // 2, len(p) - 1]) for s, p in zip(slots, prompts)]).cpu().numpy()
+    assert any(dense_calls), "no layer took the per-head form"
+    for i, p in enumerate(prompts):
+        assert_close(out[3 * i: 3 * i + 3], refs[i][[0, len(p) // 2, len(p) - 1]], dtype, f"{name} per-head prompt {i}")
+    for k in range(3):                                  # decoded tokens read the cache the prompt step wrote
+        out = engine.step([StepEntry(s, [t[k]], [0]) for s, t in zip(slots, tails)]).cpu().numpy()
+        for i, p in enumerate(prompts):
+            assert_close(out[i], refs[i][len(p) + k], dtype, f"{name} after per-head prompt {i} +{k}")
+    for s in slots:
+        engine.release(s)
+    # the same prompt with the form switched off, and in two portions (the second continues: absorbed form)
+    monkeypatch.setenv("STRATUM_LATENT_PER_HEAD", "0")
+    del dense_calls[:]
+    s = engine.acquire()
+    absorbed = engine.step([StepEntry(s, prompts[0], [299])]).cpu().numpy()
+    engine.release(s)
+    assert not any(dense_calls)
+    assert_close(absorbed, refs[0][[299]], dtype, f"{name} absorbed form")
+    monkeypatch.delenv("STRATUM_LATENT_PER_HEAD")
+    s = engine.acquire()
+    engine.step([StepEntry(s, prompts[0][:10], [])])
+    del dense_calls[:]
+    second = engine.step([StepEntry(s, prompts[0][10:], [289])]).cpu().numpy()
+    engine.release(s)
+    assert not any(dense_calls)
+    assert_close(second, refs[0][[299]], dtype, f"{name} continued portion")
