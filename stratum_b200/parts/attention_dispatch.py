@@ -82,8 +82,11 @@ def run(att, qkv: torch.Tensor, cache, step, out: torch.Tensor) -> None:
                          PAGE_TOKENS, att.window, att.scale)
 
 
-# CTAs wanted in flight on decode steps of the general attention: 148 SMs times the CTAs of four warps an SM holds
-GENERAL_TARGET_CTAS = int(os.environ.get("STRATUM_GENERAL_ATTENTION_CTAS", 148 * 4))
+# CTAs wanted on decode steps of the general attention: two to an SM of 148.  Measured at batch 8 and 4,090 cached
+# tokens, four layers (three latent, one differential): 0.166 ms with 296 against 0.209 / 0.197 / 0.191 with 148 /
+# 592 / 1,184 on a 2,048-wide model, 0.288 against 0.388 / 0.344 / 0.417 on a 4,096-wide one: more ranges are more
+# partial results for the finishing kernel to merge, fewer leave SMs idle.
+GENERAL_TARGET_CTAS = int(os.environ.get("STRATUM_GENERAL_ATTENTION_CTAS", 148 * 2))
 GENERAL_MAX_SPLITS = 64
 
 
