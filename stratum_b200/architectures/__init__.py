@@ -1,1 +1,1 @@
-from . import llama, nibelorn  # noqa: F401  (registers the architectures)
+from . import dabodra, llama, nibelorn  # noqa: F401  (registers the architectures)

@@ -1,9 +1,10 @@
 from .base import ConfigError, KeyReader, ModelConfig, read_config_json
+from .dabodra import DabodraConfig
 from .llama import LlamaConfig, RopeScaling
 from .nibelorn import NibelornConfig
 from .registry import (Architecture, architecture_name, find_architecture, register_architecture,
                        registered_architectures)
 
-__all__ = ["ConfigError", "KeyReader", "ModelConfig", "read_config_json", "LlamaConfig", "RopeScaling", "NibelornConfig",
+__all__ = ["ConfigError", "KeyReader", "ModelConfig", "read_config_json", "LlamaConfig", "RopeScaling", "NibelornConfig", "DabodraConfig",
            "Architecture", "architecture_name", "find_architecture", "register_architecture",
            "registered_architectures"]

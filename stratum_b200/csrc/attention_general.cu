@@ -11,6 +11,7 @@
 //   score_t   <- softcap * tanh(score_t / softcap)       (softcap > 0)
 //   a_m        = sum_t softmax_t(score) V_t[vh]           over the keys t in [lo, p], lo = 0 or p - window + 1
 // Values: rows of the value cache, or (v_in_k) the first v_dim values of the key rows of head (h / group) * maps.
+// sink: where given, exp(sink[h]) is one more term of every softmax's denominator (it has no key and no value).
 // combine 0 (maps = 1): out[h] = a_0.
 // combine 1 (maps = 2): o = a_0 - lambda * a_1;  o <- o / sqrt(mean(o^2) + eps) * out_scale;
 //                       o <- o * sigmoid(gate[h]) where a gate column is given (gate: q's rows, column gate_col + h).
@@ -103,6 +104,10 @@ attention_general_kernel(const GeneralAttention P) {
     }
   }
 
+  if (P.sink) {
+#pragma unroll
+    for (int m = 0; m < MAPS; m++) l_run[m] += expf(P.sink[h] - m_run[m]);
+  }
   T* op = (T*)P.out + (size_t)t * P.ldo + (size_t)h * Dv;
   if (MAPS == 1 || P.combine == 0) {
     const float inv = 1.0f / l_run[0];

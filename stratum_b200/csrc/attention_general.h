@@ -17,6 +17,7 @@ struct GeneralAttention {
   float* part_o;            // scratch of the key splits (tensor-core decode kernel)
   float* part_ml;
   const int* seq_start;     // dense keys (tensor-core kernel): first row of every sequence of the step
+  const float* sink;        // [n_heads] or null: exp(sink[h]) joins the softmax's denominator (no key, no value, not scaled)
   int ldq, ldo, bt_stride, n_tokens;
   int n_heads, group, maps;
   int qk_dim, v_dim, n_k_heads, n_v_heads, v_in_k;

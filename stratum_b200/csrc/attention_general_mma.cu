@@ -337,6 +337,7 @@ attention_general_mma_kernel(const GeneralAttention P) {
     for (int e = 0; e < 2; e++) {
       if (!row_ok[rg][e]) continue;
       if (direct) {
+        if (P.sink) l_all[e] += expf(P.sink[row_head[e]] - m_run[rg][e]);
         const float inv = 1.0f / l_all[e];
         bf16* op = (bf16*)P.out + (size_t)row_tok[rg][e] * P.ldo + (size_t)row_head[e] * Dv;
 #pragma unroll
@@ -394,6 +395,7 @@ __global__ void __launch_bounds__(128) attention_general_finish_kernel(const Gen
       weight[m][s] = w;
       l += ml[2 * s + 1] * w;
     }
+    if (P.sink) l += expf(P.sink[h] - mx);
     const float inv = 1.0f / l;
     for (int s = 0; s < S; s++) weight[m][s] *= inv;
   }

@@ -1,0 +1,62 @@
+// Norms that stand behind a sublayer instead of in front of it, and the rounding of the residual stream for the
+// sublayer that reads it.
+//
+//   norm_into_residual   x[r] (+)= y[r] / sqrt(mean(y[r]^2) + eps) * gain,  float32 in, float32 out (the residual
+//                        stream); optionally the new row is also written in bfloat16, which is what the next
+//                        sublayer's matrix products read.  y may be x itself when nothing is accumulated (a norm in
+//                        place, e.g. on freshly embedded tokens).
+//   cast_rows            out = bfloat16(x), row by row.
+//
+// One block per row; the block's shape follows from the row's length alone, so the order of a row's sum of squares
+// (and with it every bit of the result) does not depend on how many rows the step has.
+#include "common.cuh"
+
+template <bool COPY>
+__global__ void norm_into_residual_kernel(const float* y, const float* __restrict__ gain, float* x, bf16* copy,
+                                          int hidden, float eps, int accumulate) {
+  __shared__ float scratch[33];
+  const size_t row = (size_t)blockIdx.x * hidden;
+  const float* yr = y + row;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = yr[i];
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+  float* xr = x + row;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float r = yr[i] * scale * gain[i];
+    if (accumulate) r += xr[i];
+    xr[i] = r;
+    if (COPY) copy[row + i] = __float2bfloat16_rn(r);
+  }
+}
+
+static inline int row_threads(int hidden) { return hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128); }
+
+STRATUM_EXPORT int stratum_norm_into_residual(const float* y, const float* gain, float* x, void* copy, int n_rows,
+                                              int hidden, float eps, int accumulate, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (hidden < 1) return STRATUM_ERR_SHAPE;
+  if (copy)
+    norm_into_residual_kernel<true><<<n_rows, row_threads(hidden), 0, stream>>>(y, gain, x, (bf16*)copy, hidden, eps,
+                                                                               accumulate);
+  else
+    norm_into_residual_kernel<false><<<n_rows, row_threads(hidden), 0, stream>>>(y, gain, x, nullptr, hidden, eps,
+                                                                                accumulate);
+  return launch_status();
+}
+
+__global__ void cast_rows_kernel(const float* __restrict__ x, bf16* __restrict__ out, size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = __float2bfloat16_rn(x[i]);
+}
+
+STRATUM_EXPORT int stratum_cast_rows(const float* x, void* out, long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const long long blocks = (n + 255) / 256;
+  if (blocks > 0x7fffffffLL) return STRATUM_ERR_LIMIT;
+  cast_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, (bf16*)out, (size_t)n);
+  return launch_status();
+}

@@ -594,7 +594,7 @@ class _GeneralAttention(ctypes.Structure):
     _fields_ = [("q", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p), ("out", c_void_p),
                 ("token_pos", c_void_p), ("token_seq", c_void_p), ("block_table", c_void_p),
                 ("qb_seq", c_void_p), ("qb_tok0", c_void_p), ("qb_ntok", c_void_p),
-                ("part_o", c_void_p), ("part_ml", c_void_p), ("seq_start", c_void_p),
+                ("part_o", c_void_p), ("part_ml", c_void_p), ("seq_start", c_void_p), ("sink", c_void_p),
                 ("ldq", c_int), ("ldo", c_int), ("bt_stride", c_int), ("n_tokens", c_int),
                 ("n_heads", c_int), ("group", c_int), ("maps", c_int),
                 ("qk_dim", c_int), ("v_dim", c_int), ("n_k_heads", c_int), ("n_v_heads", c_int), ("v_in_k", c_int),
@@ -615,11 +615,17 @@ class AttentionShape:
 
     def __init__(self, n_heads: int, group: int, maps: int, qk_dim: int, v_dim: int, v_in_k: bool, scale: float,
                  softcap: float = 0.0, window: int = 0, temp_coef: float = 0.0, temp_every: int = 1,
-                 lam: float = 0.0, out_scale: float = 1.0, eps: float = 0.0, gate_col: int = -1):
+                 lam: float = 0.0, out_scale: float = 1.0, eps: float = 0.0, gate_col: int = -1,
+                 sink: Optional[torch.Tensor] = None):
         self.n_heads, self.group, self.maps, self.qk_dim, self.v_dim = n_heads, group, maps, qk_dim, v_dim
         self.v_in_k, self.scale, self.softcap, self.window = bool(v_in_k), scale, softcap, window
         self.temp_coef, self.temp_every, self.lam, self.out_scale = temp_coef, temp_every, lam, out_scale
         self.eps, self.gate_col = eps, gate_col
+        if sink is not None:
+            _need(sink, "sink", torch.float32)
+            if sink.numel() != n_heads:
+                raise KernelError("attention: one sink per head")
+        self.sink = sink
 
     def fill(self, p: "_GeneralAttention") -> None:
         p.n_heads, p.group, p.maps, p.qk_dim, p.v_dim = self.n_heads, self.group, self.maps, self.qk_dim, self.v_dim
@@ -628,6 +634,7 @@ class AttentionShape:
         p.v_in_k, p.window, p.combine, p.gate_col = int(self.v_in_k), self.window, int(self.maps == 2), self.gate_col
         p.temp_every, p.scale, p.softcap, p.temp_coef = self.temp_every, self.scale, self.softcap, self.temp_coef
         p.lam, p.out_scale, p.eps = self.lam, self.out_scale, self.eps
+        p.sink = None if self.sink is None else self.sink.data_ptr()
 
 
 def _general_params(shape: AttentionShape, q, k_cache, v_cache, token_pos, token_seq, block_table, out,
@@ -715,6 +722,164 @@ def attention_general_mma(shape: AttentionShape, q: torch.Tensor, k_cache: torch
     _check(f(ctypes.addressof(p), _stream()), "attention_general_mma")
     if through_scratch:
         count_launches(1)          # the finishing kernel
+
+
+# ------------------------------------------------------------------ norms behind a sublayer
+def norm_into_residual(y: torch.Tensor, gain: torch.Tensor, eps: float, x: torch.Tensor, accumulate: bool = True,
+                       copy: Optional[torch.Tensor] = None) -> None:
+    """x[r] (+)= y[r] / sqrt(mean(y[r]^2) + eps) * gain, all float32 [rows, H]; y may be x when nothing is
+    accumulated.  copy (bfloat16 [rows, H]): the new rows of x, rounded, for the products that read them."""
+    _need(y, "y", torch.float32); _need(x, "x", torch.float32); _need(gain, "gain", torch.float32)
+    if y.shape != x.shape or gain.numel() != x.shape[-1]:
+        raise KernelError("norm_into_residual: y, x and gain disagree")
+    if copy is not None:
+        _need(copy, "copy", torch.bfloat16)
+        if copy.shape != x.shape:
+            raise KernelError("norm_into_residual: copy and x disagree")
+    f = _fn("sublayer_norm", "stratum_norm_into_residual",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p])
+    _check(f(_ptr(y), _ptr(gain), _ptr(x), _ptr(copy), x.shape[0], x.shape[1], c_float(eps), int(bool(accumulate)),
+             _stream()), "norm_into_residual")
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = bfloat16(x); both contiguous and of one shape."""
+    _need(x, "x", torch.float32); _need(out, "out", torch.bfloat16)
+    if x.shape != out.shape:
+        raise KernelError("cast_rows: x and out disagree")
+    f = _fn("sublayer_norm", "stratum_cast_rows", [c_void_p, c_void_p, ctypes.c_longlong, c_void_p])
+    _check(f(_ptr(x), _ptr(out), x.numel(), _stream()), "cast_rows")
+
+
+class _QKNormRope(ctypes.Structure):
+    """Mirror of struct QKNormRope in csrc/qk_norm_rope.cu."""
+    _fields_ = [("proj", c_void_p), ("token_pos", c_void_p), ("token_seq", c_void_p), ("block_table", c_void_p),
+                ("q_gain", c_void_p), ("k_gain", c_void_p), ("inv_freq", c_void_p), ("q_out", c_void_p),
+                ("k_cache", c_void_p), ("v_cache", c_void_p),
+                ("ld", c_int), ("ldq", c_int), ("bt_stride", c_int), ("n_tokens", c_int),
+                ("n_heads", c_int), ("n_kv", c_int), ("dim", c_int), ("rot_pairs", c_int),
+                ("page_tokens", c_int), ("write_cache", c_int), ("eps", c_float), ("reserved", c_float)]
+
+
+def qk_norm_rope(proj: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor, block_table: torch.Tensor,
+                 q_gain: torch.Tensor, k_gain: torch.Tensor, inv_freq: Optional[torch.Tensor], eps: float,
+                 q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, n_heads: int, n_kv: int,
+                 dim: int, page_tokens: int, write_cache: bool) -> None:
+    """proj float32 [tokens, >= (n_heads + n_kv) * dim] holds queries then keys as projected.  The key columns go,
+    as they are, to v_cache; queries and keys are divided by the root mean square of their whole stretch (eps inside
+    the root) times a gain per column, the first 2 * len(inv_freq) dimensions of every head are rotated (pairs
+    (2i, 2i + 1), angle position * inv_freq[i]); queries go to q_out [tokens, >= n_heads * dim], keys to k_cache
+    (caches [pages, n_kv, page_tokens, dim], of q_out's dtype)."""
+    _need(proj, "proj", torch.float32, contiguous=False); _need(token_pos, "token_pos", torch.int32)
+    _need(token_seq, "token_seq", torch.int32); _need(q_gain, "q_gain", torch.float32)
+    _need(k_gain, "k_gain", torch.float32); _need(q_out, "q_out", contiguous=False)
+    if q_gain.numel() != n_heads * dim or k_gain.numel() != n_kv * dim:
+        raise KernelError("qk_norm_rope: one gain per projected column")
+    p = _QKNormRope()
+    p.proj, p.token_pos, p.token_seq = proj.data_ptr(), token_pos.data_ptr(), token_seq.data_ptr()
+    p.q_gain, p.k_gain, p.q_out = q_gain.data_ptr(), k_gain.data_ptr(), q_out.data_ptr()
+    if inv_freq is not None and inv_freq.numel():
+        _need(inv_freq, "inv_freq", torch.float32)
+        p.inv_freq, p.rot_pairs = inv_freq.data_ptr(), inv_freq.numel()
+    p.ld, p.ldq, p.n_tokens = proj.stride(0), q_out.stride(0), proj.shape[0]
+    p.n_heads, p.n_kv, p.dim, p.page_tokens, p.eps = n_heads, n_kv, dim, page_tokens, float(eps)
+    p.write_cache = int(bool(write_cache))
+    if write_cache:
+        _need(block_table, "block_table", torch.int32, contiguous=False)
+        _need(k_cache, "k_cache", q_out.dtype); _need(v_cache, "v_cache", q_out.dtype)
+        p.block_table, p.bt_stride = block_table.data_ptr(), block_table.stride(0)
+        p.k_cache, p.v_cache = k_cache.data_ptr(), v_cache.data_ptr()
+    f = _fn("qk_norm_rope", "stratum_qk_norm_rope", [c_void_p, c_int, c_void_p])
+    _check(f(ctypes.addressof(p), dtype_code(q_out.dtype), _stream()), "qk_norm_rope")
+
+
+# ------------------------------------------------------------------ the gated delta rule
+class _DeltaRule(ctypes.Structure):
+    """Mirror of struct DeltaRule in csrc/delta_rule.cu."""
+    _fields_ = [("proj", c_void_p), ("conv_w", c_void_p), ("a_log", c_void_p), ("dt_bias", c_void_p),
+                ("gain", c_void_p), ("act", c_void_p), ("o_raw", c_void_p), ("out", c_void_p), ("state", c_void_p),
+                ("token_pos", c_void_p), ("token_seq", c_void_p), ("seq_start", c_void_p), ("seq_slot", c_void_p),
+                ("ld", c_int), ("lda", c_int), ("ldo", c_int), ("n_tokens", c_int), ("n_seqs", c_int),
+                ("n_heads", c_int), ("n_kv", c_int), ("dim", c_int), ("vdim", c_int), ("taps", c_int),
+                ("state_stride", c_int), ("write_state", c_int), ("eps", c_float), ("reserved", c_float)]
+
+
+def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+               gain: torch.Tensor, act: torch.Tensor, o_raw: torch.Tensor, out: torch.Tensor, state: torch.Tensor,
+               token_pos: torch.Tensor, token_seq: torch.Tensor, seq_start: torch.Tensor, seq_slot: torch.Tensor,
+               n_heads: int, n_kv: int, dim: int, vdim: int, eps: float, write_state: bool) -> None:
+    """One step of the gated delta rule for every sequence of the step (see csrc/delta_rule.cu).  proj float32
+    [tokens, >= C + 2 n_heads + n_heads vdim] with C = 2 n_kv dim + n_heads vdim conv channels; conv_w float32
+    [C, taps]; act [tokens, >= C + 2 n_heads] and o_raw [tokens, n_heads vdim] float32 scratch; out [tokens, >=
+    n_heads vdim] in the compute dtype; state float32 [slots, n_heads dim vdim + (taps - 1) C]."""
+    for name, t in (("proj", proj), ("act", act)):
+        _need(t, name, torch.float32, contiguous=False)
+    for name, t in (("conv_w", conv_w), ("a_log", a_log), ("dt_bias", dt_bias), ("gain", gain), ("o_raw", o_raw),
+                    ("state", state)):
+        _need(t, name, torch.float32)
+    for name, t in (("token_pos", token_pos), ("token_seq", token_seq), ("seq_start", seq_start),
+                    ("seq_slot", seq_slot)):
+        _need(t, name, torch.int32)
+    _need(out, "out", contiguous=False)
+    C = 2 * n_kv * dim + n_heads * vdim
+    if conv_w.shape[0] != C or gain.numel() != vdim or a_log.numel() != n_heads or dt_bias.numel() != n_heads:
+        raise KernelError("delta_rule: weights and sizes disagree")
+    if o_raw.numel() < proj.shape[0] * n_heads * vdim or out.shape[0] != proj.shape[0]:
+        raise KernelError("delta_rule: buffers and tokens disagree")
+    p = _DeltaRule()
+    p.proj, p.conv_w, p.a_log, p.dt_bias, p.gain = (proj.data_ptr(), conv_w.data_ptr(), a_log.data_ptr(),
+                                                    dt_bias.data_ptr(), gain.data_ptr())
+    p.act, p.o_raw, p.out, p.state = act.data_ptr(), o_raw.data_ptr(), out.data_ptr(), state.data_ptr()
+    p.token_pos, p.token_seq, p.seq_start, p.seq_slot = (token_pos.data_ptr(), token_seq.data_ptr(),
+                                                         seq_start.data_ptr(), seq_slot.data_ptr())
+    p.ld, p.lda, p.ldo, p.n_tokens, p.n_seqs = proj.stride(0), act.stride(0), out.stride(0), proj.shape[0], seq_slot.numel()
+    p.n_heads, p.n_kv, p.dim, p.vdim, p.taps = n_heads, n_kv, dim, vdim, conv_w.shape[1]
+    p.state_stride, p.write_state, p.eps = state.stride(0), int(bool(write_state)), float(eps)
+    f = _fn("delta_rule", "stratum_delta_rule", [c_void_p, c_int, c_void_p])
+    _check(f(ctypes.addressof(p), dtype_code(out.dtype), _stream()), "delta_rule")
+    count_launches(2)
+
+
+# ------------------------------------------------------------------ routed experts
+class _MoeRoute(ctypes.Structure):
+    """Mirror of struct MoeRoute in csrc/moe_router.cu."""
+    _fields_ = [("x", c_void_p), ("w_router", c_void_p), ("correction", c_void_p), ("dense", c_void_p),
+                ("chosen", c_void_p), ("weights", c_void_p),
+                ("ldx", c_int), ("ldd", c_int), ("n_tokens", c_int), ("width", c_int),
+                ("n_experts", c_int), ("top", c_int), ("n_groups", c_int), ("keep", c_int),
+                ("scale", c_float), ("reserved", c_float)]
+
+
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, dense: torch.Tensor,
+              chosen: torch.Tensor, weights: torch.Tensor, top: int, n_groups: int, keep: int, scale: float) -> None:
+    """Sigmoid routing with a choice correction and groups (see csrc/moe_router.cu).  x [tokens, width] float32 or
+    bfloat16; w_router float32 [experts, width]; correction float32 [experts]; dense float32 [tokens, >= experts]
+    (weights, zeros for experts not chosen); chosen int32 and weights float32 [tokens, top]."""
+    _need(x, "x", contiguous=False); _need(w_router, "w_router", torch.float32)
+    _need(correction, "correction", torch.float32); _need(dense, "dense", torch.float32, contiguous=False)
+    _need(chosen, "chosen", torch.int32); _need(weights, "weights", torch.float32)
+    E = w_router.shape[0]
+    if w_router.shape[1] != x.shape[1] or correction.numel() != E or chosen.shape != (x.shape[0], top) \
+            or weights.shape != (x.shape[0], top) or dense.shape[0] != x.shape[0]:
+        raise KernelError("moe_route: shapes disagree")
+    p = _MoeRoute()
+    p.x, p.w_router, p.correction = x.data_ptr(), w_router.data_ptr(), correction.data_ptr()
+    p.dense, p.chosen, p.weights = dense.data_ptr(), chosen.data_ptr(), weights.data_ptr()
+    p.ldx, p.ldd, p.n_tokens, p.width = x.stride(0), dense.stride(0), x.shape[0], x.shape[1]
+    p.n_experts, p.top, p.n_groups, p.keep, p.scale = E, top, n_groups, keep, float(scale)
+    f = _fn("moe_router", "stratum_moe_route", [c_void_p, c_int, c_void_p])
+    _check(f(ctypes.addressof(p), dtype_code(x.dtype), _stream()), "moe_route")
+
+
+def scale_column_blocks(a: torch.Tensor, w: torch.Tensor, block: int, n_blocks: int) -> None:
+    """In place: a[t, e * block + j] *= w[t, e] for e < n_blocks, j < block; columns beyond stay.  w float32."""
+    _need(a, "a", contiguous=False); _need(w, "w", torch.float32, contiguous=False)
+    if a.shape[0] != w.shape[0] or a.shape[1] < block * n_blocks or w.shape[1] < n_blocks:
+        raise KernelError("scale_column_blocks: shapes disagree")
+    f = _fn("moe_router", "stratum_scale_column_blocks",
+            [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(a), dtype_code(a.dtype), a.stride(0), _ptr(w), w.stride(0), a.shape[0], block, n_blocks,
+             _stream()), "scale_column_blocks")
 
 
 def attention_mma(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, token_pos: torch.Tensor,

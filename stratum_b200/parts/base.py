@@ -82,6 +82,10 @@ class Part:
     # state row), sequences may bring no token, and query blocks come from step.query_blocks only.  A model whose
     # parts and arrangements all say so has its short prompt steps replayed; others run them launch by launch.
     replays_prompts = False
+    # a mixer or feed-forward whose forward takes `store=True` and then writes its result into the float32 tensor it
+    # is given instead of adding to it (arrangements that put a norm behind the sublayer ask for this; a part
+    # without it is handed a zeroed tensor)
+    stores_output = False
 
     def __init__(self, spec: PartSpec, runtime: Optional[Runtime]):
         self.spec = spec
@@ -104,6 +108,13 @@ class Norm(Part):
     def handover(self) -> Optional[Handover]:
         """A request for the part in front of this norm (see Handover), or None if this norm cannot be handed over."""
         return None
+
+    def add_normed(self, y: torch.Tensor, residual: torch.Tensor, accumulate: bool = True,
+                   copy: Optional[torch.Tensor] = None) -> None:
+        """The form of a norm that stands behind a sublayer: residual (+)= norm(y), float32 [T, hidden] both (y may be
+        the residual itself when nothing is accumulated); copy, where given (bfloat16 [T, hidden]), receives the new
+        residual rows rounded.  Optional."""
+        raise NotImplementedError(f"norm {self.kind!r} has no form that adds into the residual stream")
 
     def forward_heads(self, x: torch.Tensor, first_col: int, n_heads: int, head_dim: int) -> None:
         """Normalise in place, in every row of x (compute dtype), each of the n_heads stretches of head_dim

@@ -3,6 +3,7 @@ from __future__ import annotations
 
 import torch
 
+from .. import kernels as K
 from ..cache.store import LayerCache
 from .base import Arrangement
 from .registry import register_part
@@ -43,3 +44,63 @@ class PreNormResidual(Arrangement):
             return ask.result
         ff.forward(xn, x, step)
         return None
+
+
+class RoundedRows:
+    """What an `output_norm_residual` layer asks of the layer in front of it: the rows of the residual stream
+    rounded to the compute dtype, which its sublayers read.  (It stands where a layer's first norm stands in the
+    carry protocol; it cannot be handed over as a norm can, so a layer of another arrangement in front simply
+    makes nothing, and this layer rounds the rows itself.)"""
+
+    def handover(self):
+        return None
+
+
+@register_part("arrangement", "output_norm_residual")
+class OutputNormResidual(Arrangement):
+    """x += norm_a(mixer(x)); x += norm_b(feed_forward(x)): the sublayers read the residual stream itself (rounded to
+    the compute dtype for their matrix products) and each norm stands behind its part, on the part's output, before
+    that is added.  The norm's kernel adds into the stream and, on the bfloat16 path, also leaves the rounded rows
+    the next sublayer reads, so nothing else passes over the stream between two sublayers."""
+    slots = {"mixer": "mixer", "mixer_norm": "norm", "feed_forward": "feed_forward", "feed_forward_norm": "norm"}
+    optional = ("feed_forward", "feed_forward_norm")
+    carries = True
+    _asks = RoundedRows()
+
+    def accepts_carry(self, layer):
+        rt = layer.part("mixer").runtime
+        return self._asks if rt is not None and rt.dtype != torch.float32 else None
+
+    @staticmethod
+    def _run(part, xin, y, step, cache=None) -> None:
+        args = (xin, y, step) if cache is None else (xin, y, step, cache)
+        if part.stores_output:
+            part.forward(*args, store=True)
+        else:
+            y.zero_()
+            part.forward(*args)
+
+    def forward(self, layer, x: torch.Tensor, step, cache: LayerCache, carry=None, hand_to=None):
+        mixer, norm_a = layer.part("mixer"), layer.part("mixer_norm")
+        ff, norm_b = layer.part("feed_forward"), layer.part("feed_forward_norm")
+        rt = mixer.runtime
+        rounded = rt.dtype != torch.float32
+        if not rounded:
+            xin = x
+        elif isinstance(carry, torch.Tensor):
+            xin = carry
+        else:
+            xin = rt.empty(*x.shape)
+            K.cast_rows(x, xin)
+        y = rt.empty(*x.shape, dtype=torch.float32)
+        self._run(mixer, xin, y, step, cache)
+        last = ff is None or norm_b is None
+        want = rounded and (not last or isinstance(hand_to, RoundedRows))
+        copy = rt.empty(*x.shape) if want else None
+        norm_a.add_normed(y, x, True, copy)
+        if last:
+            return copy
+        self._run(ff, copy if rounded else x, y, step)
+        copy = rt.empty(*x.shape) if rounded and isinstance(hand_to, RoundedRows) else None
+        norm_b.add_normed(y, x, True, copy)
+        return copy

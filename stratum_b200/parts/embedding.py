@@ -10,14 +10,14 @@ import torch
 from .. import kernels as K
 from .base import Embedding, Head
 from .linear import STORE_F32, Linear
-from .registry import register_part
+from .registry import find_part, register_part
 from .spec import TensorSpec
 
 
 @register_part("embedding", "token_embedding")
 class TokenEmbedding(Embedding):
     """params: vocab, hidden, prefix (e.g. "model.embed_tokens."; the table is prefix + "weight"), or tensor (the
-    table's whole name)."""
+    table's whole name); norm (PartSpec of a norm the gathered rows pass, in float32 and in place, or None)."""
     replays_prompts = True
 
     def __init__(self, spec, runtime):
@@ -25,12 +25,19 @@ class TokenEmbedding(Embedding):
         self.vocab, self.hidden = int(spec["vocab"]), int(spec["hidden"])
         self.name = spec.get("tensor") or self.prefix + "weight"
         self._table: Optional[torch.Tensor] = None
+        ns = spec.get("norm")
+        self.norm = find_part("norm", ns.kind)(ns, runtime) if ns is not None else None
 
     def tensors(self) -> Dict[str, TensorSpec]:
-        return {self.name: TensorSpec((self.vocab, self.hidden))}
+        t = {self.name: TensorSpec((self.vocab, self.hidden))}
+        if self.norm is not None:
+            t.update(self.norm.tensors())
+        return t
 
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
         self._table = weights[self.name]
+        if self.norm is not None:
+            self.norm.bind(weights)
 
     def table(self) -> torch.Tensor:
         return self._table
@@ -38,6 +45,8 @@ class TokenEmbedding(Embedding):
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         out = self.runtime.empty(token_ids.numel(), self.hidden, dtype=torch.float32)
         K.embed_gather(self._table, token_ids, out)
+        if self.norm is not None:
+            self.norm.add_normed(out, out, accumulate=False)
         return out
 
 

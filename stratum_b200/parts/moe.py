@@ -1,0 +1,87 @@
+"""A mixture of experts: routed SwiGLU experts, of which every token uses a few, and a shared one.
+
+Router, in float32:  z = Wr h;  s = sigmoid(z);  the choice score of expert e is s_e + correction_e.  The experts
+form equal groups of neighbours; a group's score is the sum of its two largest choice scores, and only the experts
+of the `keep` best groups can be chosen (the others' choice scores count as -inf).  The `top` experts with the
+largest choice scores are chosen; their weights are s_e / (sum of the chosen s + 1e-20) * scale.
+
+    result = sum_chosen weight_e * Wdown_e (silu(Wgate_e h) * Wup_e h)  +  the shared expert's output (weight 1)
+
+All experts' gate and up matrices are stacked into one matrix (the shared expert's last) and all down matrices side
+by side into another, so the feed-forward is two matrix products whatever the number of experts: the first leaves
+every expert's activations side by side in a token's row, a small kernel multiplies each expert's stretch by the
+token's weight for it (zero where the expert was not chosen), and the second sums the weighted outputs.  An expert a
+token did not choose contributes exact zeros, so the result does not depend on the other tokens of the step.
+"""
+from __future__ import annotations
+
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from .. import kernels as K
+from .base import FeedForward
+from .linear import ADD_TO_F32, STORE_F32, SWIGLU, Linear
+from .mlp import interleave_rows
+from .registry import register_part
+from .spec import TensorSpec
+
+
+@register_part("feed_forward", "routed_experts")
+class RoutedExperts(FeedForward):
+    """params: hidden, n_experts, top, scale, n_groups, keep, intermediate (of an expert), shared_intermediate (of
+    the shared expert; None: none), prefix.  Tensors: router, correction, e<i>.gate / .up / .down,
+    shared.gate / .up / .down."""
+    stores_output = True
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.hidden, self.n_experts, self.top = int(spec["hidden"]), int(spec["n_experts"]), int(spec["top"])
+        self.scale = float(spec.get("scale", 1.0))
+        self.n_groups, self.keep = int(spec.get("n_groups", 1) or 1), int(spec.get("keep", 1) or 1)
+        self.ff = int(spec["intermediate"])
+        shared = spec.get("shared_intermediate")
+        self.shared_ff = int(shared) if shared else 0
+        if self.n_experts % self.n_groups or self.keep > self.n_groups \
+                or self.top > (self.n_experts // self.n_groups) * self.keep:
+            raise ValueError("routed_experts: experts, groups, keep and top do not fit together")
+        self.gate_up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+
+    def _experts(self):
+        return [f"e{i}." for i in range(self.n_experts)] + (["shared."] if self.shared_ff else [])
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        p, H = self.prefix, self.hidden
+        t = {p + "router": TensorSpec((self.n_experts, H), role="vector"),
+             p + "correction": TensorSpec((self.n_experts,), role="vector", init="zeros")}
+        for e in self._experts():
+            ff = self.shared_ff if e == "shared." else self.ff
+            t.update({p + e + "gate": TensorSpec((ff, H)), p + e + "up": TensorSpec((ff, H)),
+                      p + e + "down": TensorSpec((H, ff))})
+        return t
+
+    def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
+        p = self.prefix
+        self.router, self.correction = weights[p + "router"].contiguous(), weights[p + "correction"].contiguous()
+        names = self._experts()
+        gates = torch.cat([weights[p + e + "gate"] for e in names], dim=0)
+        ups = torch.cat([weights[p + e + "up"] for e in names], dim=0)
+        self.gate_up = Linear(self.runtime, interleave_rows(gates, ups))
+        self.down = Linear(self.runtime, torch.cat([weights[p + e + "down"] for e in names], dim=1).contiguous())
+
+    def route(self, xin: torch.Tensor):
+        """(dense weights [T, experts] with zeros for experts not chosen, chosen [T, top], their weights [T, top])."""
+        T = xin.shape[0]
+        dense = self.runtime.empty(T, self.n_experts, dtype=torch.float32)
+        chosen = self.runtime.empty(T, self.top, dtype=torch.int32)
+        weights = self.runtime.empty(T, self.top, dtype=torch.float32)
+        K.moe_route(xin, self.router, self.correction, dense, chosen, weights, self.top, self.n_groups, self.keep,
+                    self.scale)
+        return dense, chosen, weights
+
+    def forward(self, xin, residual: torch.Tensor, step, store: bool = False) -> None:
+        dense, _, _ = self.route(xin)
+        a = self.gate_up(xin, mode=SWIGLU)
+        K.scale_column_blocks(a, dense, self.ff, self.n_experts)
+        self.down(a, out=residual, mode=STORE_F32 if store else ADD_TO_F32)

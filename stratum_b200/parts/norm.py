@@ -15,20 +15,28 @@ from .spec import TensorSpec
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
-    """params: size, eps, prefix (e.g. "input_layernorm.")."""
+    """params: size, eps, prefix (e.g. "input_layernorm."; the gain is prefix + "weight") or tensor (the gain's whole
+    name), one_plus (the stored weight w is kept around zero and acts as 1 + w)."""
     replays_prompts = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.size = int(spec["size"])
         self.eps = float(spec["eps"])
+        self.name = spec.get("tensor") or self.prefix + "weight"
+        self.one_plus = bool(spec.get("one_plus", False))
         self.gain: Optional[torch.Tensor] = None
 
     def tensors(self) -> Dict[str, TensorSpec]:
-        return {self.prefix + "weight": TensorSpec((self.size,), role="vector", init="ones")}
+        return {self.name: TensorSpec((self.size,), role="vector", init="zeros" if self.one_plus else "ones")}
 
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
-        self.gain = weights[self.prefix + "weight"]
+        w = weights[self.name]
+        self.gain = (w + 1.0).contiguous() if self.one_plus else w
+
+    def add_normed(self, y: torch.Tensor, residual: torch.Tensor, accumulate: bool = True,
+                   copy: Optional[torch.Tensor] = None) -> None:
+        K.norm_into_residual(y, self.gain, self.eps, residual, accumulate, copy)
 
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         n = x.shape[0] if rows is None else rows.numel()
