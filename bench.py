@@ -4,6 +4,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers L]
     python bench.py --impl reference        # the reference arm (see below)
     python bench.py --compare nibelorn      # the Nibelorn decoder beside a Llama decoder of equal size (one JSON line)
+    python bench.py --compare dabodra       # the same for the Dabodra decoder
 
 Prints ONE JSON line.  `value` is decoded tokens per second at the given batch, with every
 sequence's cache filled to the given context at the end of the timed steps (so the timed steps
@@ -83,6 +84,32 @@ def nibelorn_config(size, n_layers):
                                      "norm": {"eps": 1e-6}, "layers": layers})
 
 
+# --compare dabodra: the same widths, heads and vocabulary; three gated-delta-rule layers to one layer of attention
+# over a window of 1,024 with a sink; eight routed experts of which a token uses two, and a shared expert, sized so
+# that a token's active feed-forward weights equal the Llama decoder's SwiGLU (2 x ff + shared = llama_inner).
+DABODRA_SIZES = {
+    "1b": {"dim": 128, "delta_dim": 128, "delta_vdim": 128, "window": 1024, "experts": 8, "top": 2, "ff": 1408,
+           "shared": 2688},
+    "8b": {"dim": 128, "delta_dim": 128, "delta_vdim": 128, "window": 1024, "experts": 8, "top": 2, "ff": 2816,
+           "shared": 5248},
+}
+
+
+def dabodra_config(size, n_layers):
+    from stratum_b200.config import DabodraConfig
+    z, d = COMPARE_SIZES[size], DABODRA_SIZES[size]
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": d["dim"], "vdim": d["dim"], "scale": d["dim"] ** -0.5,
+           "mask": {"size": d["window"]}, "rot": {"base": 10000.0, "dims": d["dim"] // 2}}
+    rec = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": d["delta_dim"], "vdim": d["delta_vdim"], "conv": 4}
+    mlp = {"kind": "moe", "router": {"experts": d["experts"], "top": d["top"], "scale": 1.0,
+                                     "groups": {"count": 4, "keep": 2}},
+           "expert": {"ff": d["ff"]}, "shared": {"ff": d["shared"]}}
+    layers = [{"type": "attention", "mixer": att, "mlp": mlp} if i % 4 == 3 else
+              {"type": "delta", "mixer": rec, "mlp": mlp} for i in range(n_layers)]
+    return DabodraConfig.from_dict({"architecture": "Dabodra", "vocab": z["vocab"], "width": z["width"],
+                                    "norm": {"eps": 1e-5}, "layers": layers})
+
+
 def llama_like(size, n_layers):
     from stratum_b200.config import LlamaConfig
     z = COMPARE_SIZES[size]
@@ -94,19 +121,49 @@ def llama_like(size, n_layers):
         "tie_word_embeddings": False, "hidden_act": "silu", "torch_dtype": "bfloat16"})
 
 
-def compare_nibelorn(args, rng):
-    """Prefill and decode throughput of the Nibelorn decoder beside a Llama decoder of equal size: one prompt of
-    --prefill-tokens, and decode steps of --batch sequences at --context tokens (random bf16 weights, device-timed
-    as the main workload is).  One JSON line."""
+def kernel_times(llm, batch, context, prefill_tokens, vocab, rng):
+    """Device time per kernel, launch by launch (no replayed graphs), of one prompt and of one decode step."""
+    import torch
+    from stratum_b200 import StepEntry, kernels
+    out = {}
+    slot = llm.acquire()
+    ids = rng.integers(0, vocab, size=prefill_tokens).tolist()
+    llm.step([StepEntry(slot, ids, [prefill_tokens - 1])])
+    llm.release(slot)
+    slot = llm.acquire()
+    kernels.profile_start()
+    llm.step([StepEntry(slot, ids, [prefill_tokens - 1])])
+    out["prompt_us"] = {n: round(t * 1e6, 1) for n, c, t in kernels.profile_report()}
+    llm.release(slot)
+    slots = [llm.acquire() for _ in range(batch)]
+    fill_to(llm, slots, context - 2, vocab, rng)
+    step = lambda: llm.step([StepEntry(s, [int(rng.integers(0, vocab))], [0]) for s in slots])     # noqa: E731
+    step()
+    kernels.profile_start()
+    step()
+    out["decode_us"] = {n: round(t * 1e6, 1) for n, c, t in kernels.profile_report()}
+    for s in slots:
+        llm.release(s)
+    torch.cuda.synchronize()
+    return out
+
+
+def compare_models(args, rng):
+    """Prefill and decode throughput of the Nibelorn or the Dabodra decoder beside a Llama decoder of equal size: one
+    prompt of --prefill-tokens, and decode steps of --batch sequences at --context tokens (random bf16 weights,
+    device-timed as the main workload is); with --kernels also the device time of every kernel of one prompt and one
+    decode step.  One JSON line."""
     import torch
     from stratum_b200 import Stratum
     n_layers = args.layers or 8
-    out = {"compare": "nibelorn", "layers": n_layers, "batch": args.batch, "context": args.context,
+    which = args.compare
+    make = nibelorn_config if which == "nibelorn" else dabodra_config
+    out = {"compare": which, "layers": n_layers, "batch": args.batch, "context": args.context,
            "prefill_tokens": args.prefill_tokens, "dtype": "bf16", "data": "synthetic: random-init weights",
            "sizes": {}}
     for size in sorted(COMPARE_SIZES):
         row = {}
-        for name, cfg in (("nibelorn", nibelorn_config(size, n_layers)), ("llama", llama_like(size, n_layers))):
+        for name, cfg in ((which, make(size, n_layers)), ("llama", llama_like(size, n_layers))):
             llm = Stratum.from_random(cfg, seed=0, dtype="bfloat16",
                                       max_tokens=max(args.batch * (args.context + 64), args.prefill_tokens + 64),
                                       max_seqs=args.batch)
@@ -117,10 +174,12 @@ def compare_nibelorn(args, rng):
                          "decode_ms_per_step": round(ms_step, 4), "launches_per_step": launches,
                          "prefill_tok_per_s": round(args.prefill_tokens * 1000.0 / pf_ms, 1),
                          "prefill_ms": round(pf_ms, 3)}
+            if args.kernels:
+                row[name]["kernels"] = kernel_times(llm, args.batch, args.context, args.prefill_tokens, cfg.vocab, rng)
             del llm
             torch.cuda.empty_cache()
-        row["decode_ratio"] = round(row["nibelorn"]["decode_tok_per_s"] / row["llama"]["decode_tok_per_s"], 3)
-        row["prefill_ratio"] = round(row["nibelorn"]["prefill_tok_per_s"] / row["llama"]["prefill_tok_per_s"], 3)
+        row["decode_ratio"] = round(row[which]["decode_tok_per_s"] / row["llama"]["decode_tok_per_s"], 3)
+        row["prefill_ratio"] = round(row[which]["prefill_tok_per_s"] / row["llama"]["prefill_tok_per_s"], 3)
         out["sizes"][size] = row
     print(json.dumps(out))
     return 0
@@ -353,9 +412,12 @@ def main() -> int:
                     help="prompt length of --prefill-only (the JSON line of the contract always uses 2,048)")
     ap.add_argument("--shape", default="llama3.1-8b", choices=["llama3.1-8b"] + sorted(OTHER_SHAPES),
                     help="layer sizes for the short lines of --decode-only / --prefill-only")
-    ap.add_argument("--compare", default=None, choices=["nibelorn"],
-                    help="instead of the main workload: prefill and decode throughput of the Nibelorn decoder beside a "
-                         "Llama decoder of equal size, at 1B-like and 8B-like layer sizes (--layers of them, default 8)")
+    ap.add_argument("--compare", default=None, choices=["nibelorn", "dabodra"],
+                    help="instead of the main workload: prefill and decode throughput of the Nibelorn or the Dabodra "
+                         "decoder beside a Llama decoder of equal size, at 1B-like and 8B-like layer sizes (--layers of "
+                         "them, default 8)")
+    ap.add_argument("--kernels", action="store_true",
+                    help="with --compare: also the device time of every kernel of one prompt and one decode step")
     ap.add_argument("--prefill-only", action="store_true",
                     help="time the 2,048-token prompt only and print a short line (for profiler runs)")
     args = ap.parse_args()
@@ -377,7 +439,7 @@ def main() -> int:
     from stratum_b200.config import LlamaConfig
 
     if args.compare:
-        return compare_nibelorn(args, np.random.default_rng(0))
+        return compare_models(args, np.random.default_rng(0))
     raw = dict(LLAMA_31_8B if args.shape == "llama3.1-8b" else OTHER_SHAPES[args.shape])
     if raw.get("rope_scaling") is None:
         raw.pop("rope_scaling", None)

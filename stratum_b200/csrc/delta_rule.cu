@@ -12,8 +12,9 @@
 // All of it is float32 whatever the compute dtype.
 //
 // The recurrence is sequential in the tokens of a sequence and independent across sequences, heads and columns of S:
-// a block owns (sequence, head, a tile of columns), a thread 32 rows of one column, so a column's sums are split over
-// dim / 32 neighbouring lanes and added by shuffles in a fixed order.  Nothing depends on how a sequence's tokens are
+// a block owns (sequence, head, a tile of columns), a thread 16 rows of one column, so a column's sums are split over
+// dim / 16 neighbouring lanes and added by shuffles in a fixed order; the tokens' k, q, v, beta and decay come through
+// a double buffer in shared memory that the next tokens fill (cp.async) while the current ones are worked on.  Nothing depends on how a sequence's tokens are
 // cut into steps or on the other sequences of a step.
 #include <math.h>
 
@@ -28,7 +29,7 @@ struct DeltaRule {
   float* act;               // [tokens][lda]: q | k | v (after prep) | beta | decay
   float* o_raw;             // [tokens][n_heads * vdim]
   void* out;                // [tokens][ldo] compute dtype
-  float* state;             // [slots][state_stride]: S [n_heads][dim][vdim], then the tail [taps - 1][channels]
+  float* state;             // [slots][state_stride]: S^T [n_heads][vdim][dim], then the tail [taps - 1][channels]
   const int* token_pos;
   const int* token_seq;
   const int* seq_start;     // [seqs + 1]
@@ -92,16 +93,28 @@ __global__ void __launch_bounds__(DR_PREP_THREADS) delta_prep_kernel(const Delta
 
 // ---------------------------------------------------------------- the recurrence
 #define DR_THREADS 128
-#define DR_ROWS 32            // rows of S a thread holds
-#define DR_PITCH 33           // floats between two lanes' stretches of k and q in shared memory (no bank conflicts)
-#define DR_CHUNK 8            // tokens staged in shared memory at a time
+#define DR_ROWS 16            // rows of S a thread holds
+#define DR_PITCH 20           // floats between two lanes' stretches of k and q in shared memory: 16-byte aligned, and
+                              // eight neighbouring lanes' float4 reads fall on different banks
+#define DR_MAX_CHUNK 16       // tokens staged in shared memory at a time, at most
 
-template <int L>              // lanes per column: dim <= 32 * L, L <= 16 (the staging fits in 48 KB)
+__device__ __forceinline__ void dr_copy4(float* dst_shared, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_shared)), "l"(src)
+               : "memory");
+}
+__device__ __forceinline__ void dr_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void dr_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// The state of a head lies in memory column by column (S^T: [vdim][dim]), so the 16 rows a thread holds are 64
+// contiguous bytes and neighbouring lanes read neighbouring stretches.
+template <int L>              // lanes per column: dim <= 16 * L
 __global__ void __launch_bounds__(DR_THREADS) delta_recur_kernel(const DeltaRule P) {
   constexpr int COLS = DR_THREADS / L;
-  __shared__ float kq_s[DR_CHUNK][2][L * DR_PITCH];
-  __shared__ float v_s[DR_CHUNK][COLS];
-  __shared__ float bg_s[DR_CHUNK][2];
+  constexpr int CHUNK = (64 / L) < DR_MAX_CHUNK ? ((64 / L) < 2 ? 2 : (64 / L)) : DR_MAX_CHUNK;
+  constexpr int KQ = L * DR_PITCH;
+  __shared__ __align__(16) float kq_s[2][CHUNK][2][KQ];
+  __shared__ float v_s[2][CHUNK][COLS];
+  __shared__ float bg_s[2][CHUNK][2];
   const int seq = blockIdx.z, h = blockIdx.y, tile = blockIdx.x;
   const int r0 = P.seq_start[seq], r1 = P.seq_start[seq + 1];
   if (r0 >= r1) return;
@@ -116,12 +129,15 @@ __global__ void __launch_bounds__(DR_THREADS) delta_recur_kernel(const DeltaRule
   }
   float* slot = P.state + (size_t)P.seq_slot[seq] * P.state_stride;
 
-  // the convolution's tail moves on by this step's tokens: one block per sequence does it, a thread per channel in
-  // the order of time, so that an entry is read before it is overwritten
-  if (tile == 0 && h == 0 && P.write_state && P.taps > 1) {
+  // the convolution's tail moves on by this step's tokens: the blocks of a sequence share the channels, a thread
+  // takes a channel through time in order, so that an entry is read before it is overwritten
+  if (P.write_state && P.taps > 1) {
     float* tail = slot + (size_t)P.n_heads * D * V;
     const int keep = P.taps - 1, n_new = r1 - r0;
-    for (int c = threadIdx.x; c < C; c += DR_THREADS)
+    const int n_blocks = gridDim.x * gridDim.y, me = blockIdx.y * gridDim.x + blockIdx.x;
+    const int per = (C + n_blocks - 1) / n_blocks;
+    const int c_end = min(C, (me + 1) * per);
+    for (int c = me * per + threadIdx.x; c < c_end; c += DR_THREADS)
       for (int i = 0; i < keep; i++) {
         const int back = keep - i;                   // this entry is the input `back` tokens before the next one
         tail[(size_t)i * C + c] = back <= n_new ? P.proj[(size_t)(r1 - back) * P.ld + c]
@@ -130,57 +146,92 @@ __global__ void __launch_bounds__(DR_THREADS) delta_recur_kernel(const DeltaRule
   }
 
   const int kv = h / (P.n_heads / P.n_kv);
-  float* Sg = slot + (size_t)h * D * V;
+  float* Sg = slot + ((size_t)h * V + (live ? j : 0)) * D + part * DR_ROWS;
+  const bool vec = D % 4 == 0 && (P.state_stride % 4) == 0 && (((uintptr_t)P.state) & 15) == 0;
   float S[DR_ROWS];
 #pragma unroll
-  for (int i = 0; i < DR_ROWS; i++) {
+  for (int i = 0; i < DR_ROWS; i += 4) {
     const int d = part * DR_ROWS + i;
-    S[i] = (live && d < D) ? Sg[(size_t)d * V + j] : 0.f;
+    if (live && vec && d + 3 < D) {
+      const float4 v4 = *reinterpret_cast<const float4*>(Sg + i);
+      S[i] = v4.x; S[i + 1] = v4.y; S[i + 2] = v4.z; S[i + 3] = v4.w;
+    } else {
+#pragma unroll
+      for (int u = 0; u < 4; u++) S[i + u] = (live && d + u < D) ? Sg[i + u] : 0.f;
+    }
   }
-  for (int c0 = r0; c0 < r1; c0 += DR_CHUNK) {
-    const int n_here = min(DR_CHUNK, r1 - c0);
-    for (int i = threadIdx.x; i < n_here * 2 * L * DR_ROWS; i += DR_THREADS) {
-      const int tok = i / (2 * L * DR_ROWS), rest = i - tok * (2 * L * DR_ROWS);
-      const int which = rest / (L * DR_ROWS), d = rest - which * (L * DR_ROWS);      // which: 0 = k, 1 = q
-      const float* a = P.act + (size_t)(c0 + tok) * P.lda + (which ? 0 : nqk) + (size_t)kv * D;
-      kq_s[tok][which][(d / DR_ROWS) * DR_PITCH + d % DR_ROWS] = d < D ? a[d] : 0.f;
+  // the dimensions beyond dim in the staging buffers stay zero: nothing below writes them
+  for (int i = threadIdx.x; i < 2 * CHUNK * 2 * KQ; i += DR_THREADS) (&kq_s[0][0][0][0])[i] = 0.f;
+  __syncthreads();
+
+  auto stage = [&](int buf, int c0) {                // ask for the tokens c0 .. of this sequence
+    const int n_here = min(CHUNK, r1 - c0);
+    for (int i = threadIdx.x; i < n_here * 2 * D; i += DR_THREADS) {
+      const int tok = i / (2 * D), rest = i - tok * 2 * D;
+      const int which = rest / D, d = rest - which * D;                          // which: 0 = k, 1 = q
+      dr_copy4(&kq_s[buf][tok][which][(d / DR_ROWS) * DR_PITCH + d % DR_ROWS],
+               P.act + (size_t)(c0 + tok) * P.lda + (which ? 0 : nqk) + (size_t)kv * D + d);
     }
     for (int i = threadIdx.x; i < n_here * COLS; i += DR_THREADS) {
       const int tok = i / COLS, cc = i - tok * COLS, jj = tile * COLS + cc;
-      v_s[tok][cc] = jj < V ? P.act[(size_t)(c0 + tok) * P.lda + 2 * nqk + (size_t)h * V + jj] : 0.f;
+      if (jj < V) dr_copy4(&v_s[buf][tok][cc], P.act + (size_t)(c0 + tok) * P.lda + 2 * nqk + (size_t)h * V + jj);
     }
     if (threadIdx.x < n_here * 2) {
-      const int tok = threadIdx.x >> 1, which = threadIdx.x & 1;      // 0 = beta, 1 = decay
-      bg_s[tok][which] = P.act[(size_t)(c0 + tok) * P.lda + C + which * P.n_heads + h];
+      const int tok = threadIdx.x >> 1, which = threadIdx.x & 1;                 // 0 = beta, 1 = decay
+      dr_copy4(&bg_s[buf][tok][which], P.act + (size_t)(c0 + tok) * P.lda + C + which * P.n_heads + h);
     }
-    __syncthreads();
+    dr_commit();
+  };
+
+  stage(0, r0);
+  int buf = 0;
+  for (int c0 = r0; c0 < r1; c0 += CHUNK, buf ^= 1) {
+    dr_wait_all();
+    __syncthreads();                                 // this chunk has landed, and the other buffer is free again
+    if (c0 + CHUNK < r1) stage(buf ^ 1, c0 + CHUNK);
+    const int n_here = min(CHUNK, r1 - c0);
     for (int tok = 0; tok < n_here; tok++) {
-      const float* kk = &kq_s[tok][0][part * DR_PITCH];
-      const float* qq = &kq_s[tok][1][part * DR_PITCH];
-      const float beta = bg_s[tok][0], decay = bg_s[tok][1];
-      float dot = 0.f;
+      const float4* kk = reinterpret_cast<const float4*>(&kq_s[buf][tok][0][part * DR_PITCH]);
+      const float4* qq = reinterpret_cast<const float4*>(&kq_s[buf][tok][1][part * DR_PITCH]);
+      const float beta = bg_s[buf][tok][0], decay = bg_s[buf][tok][1];
+      float4 k4[DR_ROWS / 4];
+      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
-      for (int i = 0; i < DR_ROWS; i++) dot = fmaf(S[i], kk[i], dot);
+      for (int i = 0; i < DR_ROWS / 4; i++) {
+        k4[i] = kk[i];
+        d0 = fmaf(S[4 * i], k4[i].x, d0); d1 = fmaf(S[4 * i + 1], k4[i].y, d1);
+        d2 = fmaf(S[4 * i + 2], k4[i].z, d2); d3 = fmaf(S[4 * i + 3], k4[i].w, d3);
+      }
+      float dot = (d0 + d1) + (d2 + d3);
 #pragma unroll
       for (int o = 1; o < L; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      const float u = beta * (v_s[tok][col] - decay * dot);
-      float oq = 0.f;
+      const float u = beta * (v_s[buf][tok][col] - decay * dot);
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-      for (int i = 0; i < DR_ROWS; i++) {
-        S[i] = fmaf(kk[i], u, decay * S[i]);
-        oq = fmaf(S[i], qq[i], oq);
+      for (int i = 0; i < DR_ROWS / 4; i++) {
+        const float4 q4 = qq[i];
+        S[4 * i] = fmaf(k4[i].x, u, decay * S[4 * i]);         o0 = fmaf(S[4 * i], q4.x, o0);
+        S[4 * i + 1] = fmaf(k4[i].y, u, decay * S[4 * i + 1]); o1 = fmaf(S[4 * i + 1], q4.y, o1);
+        S[4 * i + 2] = fmaf(k4[i].z, u, decay * S[4 * i + 2]); o2 = fmaf(S[4 * i + 2], q4.z, o2);
+        S[4 * i + 3] = fmaf(k4[i].w, u, decay * S[4 * i + 3]); o3 = fmaf(S[4 * i + 3], q4.w, o3);
       }
+      float oq = (o0 + o1) + (o2 + o3);
 #pragma unroll
       for (int o = 1; o < L; o <<= 1) oq += __shfl_xor_sync(0xffffffffu, oq, o);
       if (part == 0 && live) P.o_raw[(size_t)(c0 + tok) * P.n_heads * V + (size_t)h * V + j] = oq;
     }
-    __syncthreads();
   }
   if (P.write_state && live) {
 #pragma unroll
-    for (int i = 0; i < DR_ROWS; i++) {
+    for (int i = 0; i < DR_ROWS; i += 4) {
       const int d = part * DR_ROWS + i;
-      if (d < D) Sg[(size_t)d * V + j] = S[i];
+      if (vec && d + 3 < D) {
+        *reinterpret_cast<float4*>(Sg + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+      } else {
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+          if (d + u < D) Sg[i + u] = S[i + u];
+      }
     }
   }
 }
@@ -230,7 +281,7 @@ STRATUM_EXPORT int stratum_delta_rule(const DeltaRule* params, int out_dtype, cu
   int st = launch_status();
   if (st) return st;
   int L = 1;
-  while (32 * L < P.dim) L <<= 1;
+  while (DR_ROWS * L < P.dim) L <<= 1;
   const int cols = DR_THREADS / L;
   if (P.n_heads > 65535 || P.n_seqs > 65535) return STRATUM_ERR_LIMIT;
   const dim3 grid((P.vdim + cols - 1) / cols, P.n_heads, P.n_seqs);
@@ -239,7 +290,8 @@ STRATUM_EXPORT int stratum_delta_rule(const DeltaRule* params, int out_dtype, cu
     case 2: delta_recur_kernel<2><<<grid, DR_THREADS, 0, stream>>>(P); break;
     case 4: delta_recur_kernel<4><<<grid, DR_THREADS, 0, stream>>>(P); break;
     case 8: delta_recur_kernel<8><<<grid, DR_THREADS, 0, stream>>>(P); break;
-    default: delta_recur_kernel<16><<<grid, DR_THREADS, 0, stream>>>(P); break;
+    case 16: delta_recur_kernel<16><<<grid, DR_THREADS, 0, stream>>>(P); break;
+    default: delta_recur_kernel<32><<<grid, DR_THREADS, 0, stream>>>(P); break;
   }
   st = launch_status();
   if (st) return st;

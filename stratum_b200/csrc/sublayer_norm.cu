@@ -33,12 +33,57 @@ __global__ void norm_into_residual_kernel(const float* y, const float* __restric
   }
 }
 
+// The same with four values per thread and turn (rows of a multiple of four values, 16-byte aligned).
+template <bool COPY>
+__global__ void norm_into_residual_vec_kernel(const float* y, const float* __restrict__ gain, float* x, bf16* copy,
+                                              int hidden, float eps, int accumulate) {
+  __shared__ float scratch[33];
+  const size_t row = (size_t)blockIdx.x * hidden;
+  const float4* yr = reinterpret_cast<const float4*>(y + row);
+  const int n4 = hidden >> 2;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+    const float4 v = yr[i];
+    ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+  float4* xr = reinterpret_cast<float4*>(x + row);
+  for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+    const float4 v = yr[i], g = reinterpret_cast<const float4*>(gain)[i];
+    float4 r = make_float4(v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w);
+    if (accumulate) {
+      const float4 o = xr[i];
+      r.x += o.x; r.y += o.y; r.z += o.z; r.w += o.w;
+    }
+    xr[i] = r;
+    if (COPY) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(r.x, r.y), hi = __floats2bfloat162_rn(r.z, r.w);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      reinterpret_cast<uint2*>(copy + row)[i] = pk;
+    }
+  }
+}
+
 static inline int row_threads(int hidden) { return hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128); }
 
 STRATUM_EXPORT int stratum_norm_into_residual(const float* y, const float* gain, float* x, void* copy, int n_rows,
                                               int hidden, float eps, int accumulate, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (hidden < 1) return STRATUM_ERR_SHAPE;
+  const bool vec = hidden % 4 == 0 && ((((uintptr_t)y | (uintptr_t)gain | (uintptr_t)x | (uintptr_t)copy) & 15) == 0);
+  if (vec) {
+    // (the choice depends on the row's length and on alignment alone, which a model's buffers share from step to step)
+    if (copy)
+      norm_into_residual_vec_kernel<true><<<n_rows, row_threads(hidden / 4), 0, stream>>>(y, gain, x, (bf16*)copy, hidden,
+                                                                                         eps, accumulate);
+    else
+      norm_into_residual_vec_kernel<false><<<n_rows, row_threads(hidden / 4), 0, stream>>>(y, gain, x, nullptr, hidden,
+                                                                                          eps, accumulate);
+    return launch_status();
+  }
   if (copy)
     norm_into_residual_kernel<true><<<n_rows, row_threads(hidden), 0, stream>>>(y, gain, x, (bf16*)copy, hidden, eps,
                                                                                accumulate);

@@ -882,6 +882,46 @@ def scale_column_blocks(a: torch.Tensor, w: torch.Tensor, block: int, n_blocks: 
              _stream()), "scale_column_blocks")
 
 
+def moe_group(chosen: torch.Tensor, n_experts: int):
+    """The (token, choice) pairs of chosen [tokens, top] in the order of their experts, within an expert in the order
+    of the tokens: (counts int32 [experts], order int32 [pairs]: the pair at every place, where int32 [pairs]: the
+    place of every pair), all on the device."""
+    _need(chosen, "chosen", torch.int32)
+    n = chosen.numel()
+    counts = torch.empty(n_experts, dtype=torch.int32, device=chosen.device)
+    order = torch.empty(n, dtype=torch.int32, device=chosen.device)
+    where = torch.empty(n, dtype=torch.int32, device=chosen.device)
+    f = _fn("moe_router", "stratum_moe_group", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(chosen), n, n_experts, _ptr(counts), _ptr(order), _ptr(where), _stream()), "moe_group")
+    count_launches(1)
+    return counts, order, where
+
+
+def gather_rows(x: torch.Tensor, order: torch.Tensor, top: int, out: torch.Tensor) -> None:
+    """out[r] = x[order[r] // top]; out contiguous [len(order), width] of x's dtype."""
+    _need(x, "x", contiguous=False); _need(order, "order", torch.int32); _need(out, "out", x.dtype)
+    if out.shape != (order.numel(), x.shape[1]):
+        raise KernelError("gather_rows: shapes disagree")
+    f = _fn("moe_router", "stratum_gather_rows",
+            [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), dtype_code(x.dtype), x.stride(0), _ptr(order), top, _ptr(out), out.shape[0], x.shape[1],
+             _stream()), "gather_rows")
+
+
+def moe_combine(outs: torch.Tensor, where: torch.Tensor, weights: torch.Tensor, y: torch.Tensor,
+                accumulate: bool) -> None:
+    """y[t] (+)= sum_k weights[t, k] * outs[where[t * top + k]]; outs float32 [pairs, width], y float32 [tokens, width]."""
+    _need(outs, "outs", torch.float32); _need(where, "where", torch.int32); _need(weights, "weights", torch.float32)
+    _need(y, "y", torch.float32)
+    T, top = weights.shape
+    if where.numel() != T * top or outs.shape != (T * top, y.shape[1]) or y.shape[0] != T:
+        raise KernelError("moe_combine: shapes disagree")
+    f = _fn("moe_router", "stratum_moe_combine",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(outs), _ptr(where), _ptr(weights), _ptr(y), T, top, y.shape[1], int(bool(accumulate)), _stream()),
+           "moe_combine")
+
+
 def attention_mma(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, token_pos: torch.Tensor,
                   token_seq: torch.Tensor, block_table: torch.Tensor, qblocks, tokens_per_block: int,
                   out: torch.Tensor, part_o: Optional[torch.Tensor], part_ml: Optional[torch.Tensor], n_q: int,

@@ -90,11 +90,15 @@ GENERAL_TARGET_CTAS = int(os.environ.get("STRATUM_GENERAL_ATTENTION_CTAS", 148 *
 GENERAL_MAX_SPLITS = 64
 
 
-def plan_general_splits(n_items: int, max_len: int):
-    """(n_splits, keys per split) for decode steps of the general attention: whole pages per split."""
+def plan_general_splits(n_items: int, max_len: int, window: int = 0):
+    """(n_splits, keys per split) for decode steps of the general attention: whole pages per split.  Ranges are
+    counted from position 0 for every sequence; with a window only the last ones hold keys a row can see (the others
+    leave at once), so the ranges are sized to cut the window's stretch, not the whole sequence, into enough pieces."""
     pages = max(1, (max_len + PAGE_TOKENS - 1) // PAGE_TOKENS)
-    want = max(1, min(pages, GENERAL_MAX_SPLITS, (GENERAL_TARGET_CTAS + n_items - 1) // n_items))
-    chunk = ((pages + want - 1) // want) * PAGE_TOKENS
+    seen = pages if window <= 0 else min(pages, (window + PAGE_TOKENS - 1) // PAGE_TOKENS + 1)
+    want = max(1, min(seen, GENERAL_MAX_SPLITS, (GENERAL_TARGET_CTAS + n_items - 1) // n_items))
+    per = max((seen + want - 1) // want, (pages + GENERAL_MAX_SPLITS - 1) // GENERAL_MAX_SPLITS)
+    chunk = per * PAGE_TOKENS
     return (max_len + chunk - 1) // chunk, chunk
 
 
@@ -128,7 +132,7 @@ def run_general(att, shape, q: torch.Tensor, cache, step, out: torch.Tensor) -> 
     row_groups = 1
     if step.all_single:
         qblocks = None
-        n_splits, chunk = plan_general_splits(step.n_tokens * streams, step.max_len)
+        n_splits, chunk = plan_general_splits(step.n_tokens * streams, step.max_len, shape.window)
     else:
         # prompts: a CTA takes several groups of 16 rows through every tile of keys, which then comes from L2 once
         row_groups = K.attention_general_mma_row_groups(shape.v_dim)

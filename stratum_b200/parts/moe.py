@@ -7,14 +7,25 @@ largest choice scores are chosen; their weights are s_e / (sum of the chosen s +
 
     result = sum_chosen weight_e * Wdown_e (silu(Wgate_e h) * Wup_e h)  +  the shared expert's output (weight 1)
 
-All experts' gate and up matrices are stacked into one matrix (the shared expert's last) and all down matrices side
-by side into another, so the feed-forward is two matrix products whatever the number of experts: the first leaves
-every expert's activations side by side in a token's row, a small kernel multiplies each expert's stretch by the
-token's weight for it (zero where the expert was not chosen), and the second sums the weighted outputs.  An expert a
-token did not choose contributes exact zeros, so the result does not depend on the other tokens of the step.
+Two ways to run the experts, chosen by the step's size:
+
+* few tokens (decode steps, short prompts): all experts' gate and up matrices are stacked into one matrix (the shared
+  expert's last) and all down matrices side by side into another, so the feed-forward is two matrix products whatever
+  the number of experts: the first leaves every expert's activations side by side in a token's row, a small kernel
+  multiplies each expert's stretch by the token's weight for it (zero where the expert was not chosen), and the second
+  sums the weighted outputs.  A step of a few tokens reads most experts' weights anyway, and nothing on this way
+  depends on a number the host would have to wait for, so it runs inside a captured decode step.
+* many tokens (prompts): the (token, choice) pairs are put in the order of their experts on the device, the host reads
+  the experts' counts (one small copy per layer), every expert runs its two products on its own stretch of gathered
+  rows, and each token adds up its experts' outputs times its weights in the order of its choices; the shared expert
+  runs on all rows.  Only the chosen experts' arithmetic is done.
+
+Either way an expert a token did not choose contributes nothing, and a token's sum has a fixed order, so the result
+does not depend on the other tokens of the step beyond the rounding of the products.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, Mapping, Optional
 
 import torch
@@ -25,6 +36,11 @@ from .linear import ADD_TO_F32, STORE_F32, SWIGLU, Linear
 from .mlp import interleave_rows
 from .registry import register_part
 from .spec import TensorSpec
+
+
+# rows an expert gets on average from which a prompt step takes the grouped way (T * top / experts); measured on layer
+# sizes of a 1B-like and an 8B-like model, see the design notes.  STRATUM_MOE_GROUPED_MIN_ROWS sets it (measurements).
+GROUPED_MIN_ROWS = int(os.environ.get("STRATUM_MOE_GROUPED_MIN_ROWS", 96))
 
 
 @register_part("feed_forward", "routed_experts")
@@ -67,8 +83,15 @@ class RoutedExperts(FeedForward):
         names = self._experts()
         gates = torch.cat([weights[p + e + "gate"] for e in names], dim=0)
         ups = torch.cat([weights[p + e + "up"] for e in names], dim=0)
-        self.gate_up = Linear(self.runtime, interleave_rows(gates, ups))
+        stacked = interleave_rows(gates, ups)
+        self.gate_up = Linear(self.runtime, stacked)
         self.down = Linear(self.runtime, torch.cat([weights[p + e + "down"] for e in names], dim=1).contiguous())
+        # the grouped way: every expert's matrices by themselves (gate|up: stretches of the stacked rows; down: the
+        # tensors as loaded, since a stretch of the stacked matrix's columns is not a matrix a product can take)
+        first = [2 * self.ff * i for i in range(self.n_experts)] + [2 * self.ff * self.n_experts]
+        sizes = [2 * self.ff] * self.n_experts + [2 * self.shared_ff]
+        self.gate_up_of = [Linear(self.runtime, stacked[a:a + n]) for a, n in zip(first, sizes) if n]
+        self.down_of = [Linear(self.runtime, weights[p + e + "down"].contiguous()) for e in names]
 
     def route(self, xin: torch.Tensor):
         """(dense weights [T, experts] with zeros for experts not chosen, chosen [T, top], their weights [T, top])."""
@@ -80,8 +103,32 @@ class RoutedExperts(FeedForward):
                     self.scale)
         return dense, chosen, weights
 
+    def grouped(self, step, n_tokens: int) -> bool:
+        """Whether this step takes the grouped way: a prompt step (never a step that may be captured and replayed: the
+        host waits for the experts' counts) whose experts get enough rows each."""
+        return (not step.all_single and self.top < self.n_experts
+                and n_tokens * self.top >= GROUPED_MIN_ROWS * self.n_experts)
+
     def forward(self, xin, residual: torch.Tensor, step, store: bool = False) -> None:
-        dense, _, _ = self.route(xin)
-        a = self.gate_up(xin, mode=SWIGLU)
-        K.scale_column_blocks(a, dense, self.ff, self.n_experts)
-        self.down(a, out=residual, mode=STORE_F32 if store else ADD_TO_F32)
+        dense, chosen, weights = self.route(xin)
+        T = xin.shape[0]
+        if not self.grouped(step, T):
+            a = self.gate_up(xin, mode=SWIGLU)
+            K.scale_column_blocks(a, dense, self.ff, self.n_experts)
+            self.down(a, out=residual, mode=STORE_F32 if store else ADD_TO_F32)
+            return
+        counts, order, where = K.moe_group(chosen, self.n_experts)
+        counts = counts.tolist()                          # the host waits here, once per layer
+        rows = self.runtime.empty(T * self.top, self.hidden)
+        K.gather_rows(xin, order, self.top, rows)
+        outs = self.runtime.empty(T * self.top, self.hidden, dtype=torch.float32)
+        at = 0
+        for e, n in enumerate(counts):
+            if n:
+                a = self.gate_up_of[e](rows[at:at + n], mode=SWIGLU)
+                self.down_of[e](a, out=outs[at:at + n], mode=STORE_F32)
+                at += n
+        if self.shared_ff:
+            a = self.gate_up_of[self.n_experts](xin, mode=SWIGLU)
+            self.down_of[self.n_experts](a, out=residual, mode=STORE_F32 if store else ADD_TO_F32)
+        K.moe_combine(outs, where, weights, residual, accumulate=bool(self.shared_ff) or not store)

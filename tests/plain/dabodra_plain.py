@@ -21,7 +21,6 @@ acts as h @ W.T.
 """
 from __future__ import annotations
 
-import math
 from typing import Dict, List
 
 import numpy as np
@@ -78,9 +77,10 @@ def windowed_sink_attention(h, w: Dict[str, np.ndarray], m: dict, eps: float):
     v = k_raw.reshape(T, G, D)
     q = rms_norm(q_raw, w["q.norm"], eps).reshape(T, H, D)
     k = rms_norm(k_raw, w["k.norm"], eps).reshape(T, G, D)
-    q = rotate_pairs(q, pos, m["rot"]["base"], m["rot"]["dims"])
-    k = rotate_pairs(k, pos, m["rot"]["base"], m["rot"]["dims"])
-    window = m["mask"]["size"]
+    if m.get("rot") and m["rot"]["dims"]:
+        q = rotate_pairs(q, pos, m["rot"]["base"], m["rot"]["dims"])
+        k = rotate_pairs(k, pos, m["rot"]["base"], m["rot"]["dims"])
+    window = m["mask"]["size"] if m.get("mask") else T
     out = np.zeros((T, H, D), F64)
     for head in range(H):
         kv = head // (H // G)
@@ -101,7 +101,7 @@ def causal_conv(x, taps):
     x, taps = np.asarray(x, F64), np.asarray(taps, F64)
     n = taps.shape[1]
     y = np.zeros_like(x)
-    for i in range(n):
+    for i in range(min(n, x.shape[0])):
         y[i:] += x[:x.shape[0] - i] * taps[:, n - 1 - i][None, :]
     return y
 
@@ -140,8 +140,10 @@ def expert(h, w: Dict[str, np.ndarray], prefix: str):
     return linear(silu(linear(h, w[prefix + "gate"])) * linear(h, w[prefix + "up"]), w[prefix + "down"])
 
 
-def route(h, w_router, correction, r: dict):
-    """(chosen experts [T, top], their weights [T, top]); r: experts, top, scale, groups.count, groups.keep."""
+def route(h, w_router, correction, r: dict, margins: List[float] = None):
+    """(chosen experts [T, top], their weights [T, top]); r: experts, top, scale, groups.count, groups.keep.
+    margins (a list) receives, per token, by how much the last choice made (of a group, of an expert) led the best
+    one not made: a test keeps away from inputs on which rounding could make another choice."""
     E, top = r["experts"], r["top"]
     n_groups, keep = r["groups"]["count"], r["groups"]["keep"]
     s = sigmoid(linear(h, w_router))
@@ -157,16 +159,23 @@ def route(h, w_router, correction, r: dict):
         allowed = np.full(E, -np.inf)
         for gi in best:
             allowed[gi * per:(gi + 1) * per] = c[t, gi * per:(gi + 1) * per]
-        idx = np.argsort(-allowed, kind="stable")[:top]
+        order = np.argsort(-allowed, kind="stable")
+        idx = order[:top]
+        if margins is not None:
+            ranked = np.sort(score)[::-1]
+            if keep < n_groups:
+                margins.append(float(ranked[keep - 1] - ranked[keep]))
+            if top < len(order) and np.isfinite(allowed[order[top]]):
+                margins.append(float(allowed[order[top - 1]] - allowed[order[top]]))
         chosen[t] = idx
         weights[t] = s[t, idx] / (s[t, idx].sum() + 1e-20) * F64(r["scale"])
     return chosen, weights
 
 
-def routed_experts(h, w: Dict[str, np.ndarray], mlp: dict):
+def routed_experts(h, w: Dict[str, np.ndarray], mlp: dict, margins: List[float] = None):
     """w: router, correction, e<i>.gate/up/down, shared.gate/up/down."""
-    chosen, weights = route(h, w["router"], w["correction"], mlp["router"])
-    out = expert(h, w, "shared.")
+    chosen, weights = route(h, w["router"], w["correction"], mlp["router"], margins)
+    out = expert(h, w, "shared.") if mlp.get("shared") else np.zeros_like(np.asarray(h, F64))
     per_expert = [expert(h, w, f"e{e}.") for e in range(mlp["router"]["experts"])]
     for t in range(h.shape[0]):
         for e, wt in zip(chosen[t], weights[t]):
@@ -178,8 +187,10 @@ def sub(tensors: Dict[str, np.ndarray], prefix: str) -> Dict[str, np.ndarray]:
     return {k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def forward(config: dict, tensors: Dict[str, np.ndarray], tokens, after_layers: List[np.ndarray] = None):
-    """Logits [T, vocab] of one whole sequence; after_layers (a list) receives the residual stream after every layer."""
+def forward(config: dict, tensors: Dict[str, np.ndarray], tokens, after_layers: List[np.ndarray] = None,
+            margins: List[float] = None):
+    """Logits [T, vocab] of one whole sequence; after_layers (a list) receives the residual stream after every layer,
+    margins (a list) the routers' margins (see route)."""
     eps = config["norm"]["eps"]
     x = one_plus_norm(np.asarray(tensors["embed"], F64)[np.asarray(tokens)], tensors["embed.norm"], eps)
     for i, layer in enumerate(config["layers"]):
@@ -193,7 +204,7 @@ def forward(config: dict, tensors: Dict[str, np.ndarray], tokens, after_layers: 
             raise ValueError(layer["type"])
         x = x + one_plus_norm(y, tensors[p + "norm1"], eps)
         if layer.get("mlp") is not None:
-            y = routed_experts(x, sub(tensors, p + "mlp."), layer["mlp"])
+            y = routed_experts(x, sub(tensors, p + "mlp."), layer["mlp"], margins)
             x = x + one_plus_norm(y, tensors[p + "norm2"], eps)
         if after_layers is not None:
             after_layers.append(x.copy())
