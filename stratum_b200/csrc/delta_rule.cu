@@ -102,6 +102,10 @@ __device__ __forceinline__ void dr_copy4(float* dst_shared, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_shared)), "l"(src)
                : "memory");
 }
+__device__ __forceinline__ void dr_copy16(float* dst_shared, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_shared)), "l"(src)
+               : "memory");
+}
 __device__ __forceinline__ void dr_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void dr_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
@@ -164,13 +168,22 @@ __global__ void __launch_bounds__(DR_THREADS) delta_recur_kernel(const DeltaRule
   for (int i = threadIdx.x; i < 2 * CHUNK * 2 * KQ; i += DR_THREADS) (&kq_s[0][0][0][0])[i] = 0.f;
   __syncthreads();
 
+  const bool vec_act = D % 4 == 0 && P.lda % 4 == 0 && (((uintptr_t)P.act) & 15) == 0;
   auto stage = [&](int buf, int c0) {                // ask for the tokens c0 .. of this sequence
     const int n_here = min(CHUNK, r1 - c0);
-    for (int i = threadIdx.x; i < n_here * 2 * D; i += DR_THREADS) {
-      const int tok = i / (2 * D), rest = i - tok * 2 * D;
-      const int which = rest / D, d = rest - which * D;                          // which: 0 = k, 1 = q
-      dr_copy4(&kq_s[buf][tok][which][(d / DR_ROWS) * DR_PITCH + d % DR_ROWS],
-               P.act + (size_t)(c0 + tok) * P.lda + (which ? 0 : nqk) + (size_t)kv * D + d);
+    for (int tok = 0; tok < n_here; tok++) {
+      const float* a = P.act + (size_t)(c0 + tok) * P.lda + (size_t)kv * D;
+      if (vec_act) {
+        for (int d = 4 * threadIdx.x; d < 2 * D; d += 4 * DR_THREADS) {          // k, then q
+          const int which = d >= D, dd = d - which * D;
+          dr_copy16(&kq_s[buf][tok][which][(dd / DR_ROWS) * DR_PITCH + dd % DR_ROWS], a + (which ? 0 : nqk) + dd);
+        }
+      } else {
+        for (int d = threadIdx.x; d < 2 * D; d += DR_THREADS) {
+          const int which = d >= D, dd = d - which * D;
+          dr_copy4(&kq_s[buf][tok][which][(dd / DR_ROWS) * DR_PITCH + dd % DR_ROWS], a + (which ? 0 : nqk) + dd);
+        }
+      }
     }
     for (int i = threadIdx.x; i < n_here * COLS; i += DR_THREADS) {
       const int tok = i / COLS, cc = i - tok * COLS, jj = tile * COLS + cc;
@@ -183,6 +196,9 @@ __global__ void __launch_bounds__(DR_THREADS) delta_recur_kernel(const DeltaRule
     dr_commit();
   };
 
+  // Per token the two sums over a column, S^T k and S^T q, are taken from the state as the token finds it, together
+  // and with one round of shuffles; the read-out after the token's own write follows from them:
+  //   S' = decay S + k u^T,  u = beta (v - decay S^T k)   =>   S'^T q = decay S^T q + (k . q) u.
   stage(0, r0);
   int buf = 0;
   for (int c0 = r0; c0 < r1; c0 += CHUNK, buf ^= 1) {
@@ -193,32 +209,37 @@ __global__ void __launch_bounds__(DR_THREADS) delta_recur_kernel(const DeltaRule
     for (int tok = 0; tok < n_here; tok++) {
       const float4* kk = reinterpret_cast<const float4*>(&kq_s[buf][tok][0][part * DR_PITCH]);
       const float4* qq = reinterpret_cast<const float4*>(&kq_s[buf][tok][1][part * DR_PITCH]);
-      const float beta = bg_s[buf][tok][0], decay = bg_s[buf][tok][1];
+      const float beta = bg_s[buf][tok][0], decay = bg_s[buf][tok][1], vj = v_s[buf][tok][col];
       float4 k4[DR_ROWS / 4];
-      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+      float sk[4] = {0.f, 0.f, 0.f, 0.f}, sq[4] = {0.f, 0.f, 0.f, 0.f}, kq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < DR_ROWS / 4; i++) {
         k4[i] = kk[i];
-        d0 = fmaf(S[4 * i], k4[i].x, d0); d1 = fmaf(S[4 * i + 1], k4[i].y, d1);
-        d2 = fmaf(S[4 * i + 2], k4[i].z, d2); d3 = fmaf(S[4 * i + 3], k4[i].w, d3);
+        const float4 q4 = qq[i];
+        sk[0] = fmaf(S[4 * i], k4[i].x, sk[0]); sk[1] = fmaf(S[4 * i + 1], k4[i].y, sk[1]);
+        sk[2] = fmaf(S[4 * i + 2], k4[i].z, sk[2]); sk[3] = fmaf(S[4 * i + 3], k4[i].w, sk[3]);
+        sq[0] = fmaf(S[4 * i], q4.x, sq[0]); sq[1] = fmaf(S[4 * i + 1], q4.y, sq[1]);
+        sq[2] = fmaf(S[4 * i + 2], q4.z, sq[2]); sq[3] = fmaf(S[4 * i + 3], q4.w, sq[3]);
+        kq[0] = fmaf(k4[i].x, q4.x, kq[0]); kq[1] = fmaf(k4[i].y, q4.y, kq[1]);
+        kq[2] = fmaf(k4[i].z, q4.z, kq[2]); kq[3] = fmaf(k4[i].w, q4.w, kq[3]);
       }
-      float dot = (d0 + d1) + (d2 + d3);
+      float a = (sk[0] + sk[1]) + (sk[2] + sk[3]), b = (sq[0] + sq[1]) + (sq[2] + sq[3]);
+      float c = (kq[0] + kq[1]) + (kq[2] + kq[3]);
 #pragma unroll
-      for (int o = 1; o < L; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      const float u = beta * (v_s[buf][tok][col] - decay * dot);
-      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+      for (int o = 1; o < L; o <<= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, o);
+        b += __shfl_xor_sync(0xffffffffu, b, o);
+        c += __shfl_xor_sync(0xffffffffu, c, o);
+      }
+      const float u = beta * (vj - decay * a);
 #pragma unroll
       for (int i = 0; i < DR_ROWS / 4; i++) {
-        const float4 q4 = qq[i];
-        S[4 * i] = fmaf(k4[i].x, u, decay * S[4 * i]);         o0 = fmaf(S[4 * i], q4.x, o0);
-        S[4 * i + 1] = fmaf(k4[i].y, u, decay * S[4 * i + 1]); o1 = fmaf(S[4 * i + 1], q4.y, o1);
-        S[4 * i + 2] = fmaf(k4[i].z, u, decay * S[4 * i + 2]); o2 = fmaf(S[4 * i + 2], q4.z, o2);
-        S[4 * i + 3] = fmaf(k4[i].w, u, decay * S[4 * i + 3]); o3 = fmaf(S[4 * i + 3], q4.w, o3);
+        S[4 * i] = fmaf(k4[i].x, u, decay * S[4 * i]);
+        S[4 * i + 1] = fmaf(k4[i].y, u, decay * S[4 * i + 1]);
+        S[4 * i + 2] = fmaf(k4[i].z, u, decay * S[4 * i + 2]);
+        S[4 * i + 3] = fmaf(k4[i].w, u, decay * S[4 * i + 3]);
       }
-      float oq = (o0 + o1) + (o2 + o3);
-#pragma unroll
-      for (int o = 1; o < L; o <<= 1) oq += __shfl_xor_sync(0xffffffffu, oq, o);
-      if (part == 0 && live) P.o_raw[(size_t)(c0 + tok) * P.n_heads * V + (size_t)h * V + j] = oq;
+      if (part == 0 && live) P.o_raw[(size_t)(c0 + tok) * P.n_heads * V + (size_t)h * V + j] = fmaf(c, u, decay * b);
     }
   }
   if (P.write_state && live) {
