@@ -409,7 +409,7 @@ def main() -> int:
                     help="the baseline's other workloads through Stratum.generate: 8 unequal prompts of 64..2048 "
                          "tokens + 256 new tokens (Llama-2-7B), or 64 prompts of 512 + 512 new tokens (Llama-3.2-1B)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
-                    help="prompt length of --prefill-only (the JSON line of the contract always uses 2,048)")
+                    help="prompt length of --prefill-only (the default JSON line always uses 2,048)")
     ap.add_argument("--shape", default="llama3.1-8b", choices=["llama3.1-8b"] + sorted(OTHER_SHAPES),
                     help="layer sizes for the short lines of --decode-only / --prefill-only")
     ap.add_argument("--compare", default=None, choices=["nibelorn", "dabodra"],
