@@ -12,10 +12,11 @@
 // All of it is float32 whatever the compute dtype.
 //
 // The recurrence is sequential in the tokens of a sequence and independent across sequences, heads and columns of S:
-// a block owns (sequence, head, a tile of columns), a thread 16 rows of one column, so a column's sums are split over
-// dim / 16 neighbouring lanes and added by shuffles in a fixed order; the tokens' k, q, v, beta and decay come through
-// a double buffer in shared memory that the next tokens fill (cp.async) while the current ones are worked on.  Nothing depends on how a sequence's tokens are
-// cut into steps or on the other sequences of a step.
+// a block owns (sequence, head, a tile of columns), a thread 4, 8 or 16 rows of one column, so a column's sums are
+// split over neighbouring lanes and added by shuffles in a fixed order; the tokens' k, q, v, beta, decay and k . q
+// come through a double buffer in shared memory that the next tokens fill (cp.async) while the current ones are
+// worked on.  Nothing depends on how a sequence's tokens are cut into steps; the other sequences of a step decide
+// at most how many rows a lane holds, that is, the order in which a column's sums are added.
 #include <math.h>
 
 #include "common.cuh"
@@ -26,7 +27,7 @@ struct DeltaRule {
   const float* a_log;       // [n_heads]
   const float* dt_bias;     // [n_heads]
   const float* gain;        // [vdim]
-  float* act;               // [tokens][lda]: q | k | v (after prep) | beta | decay
+  float* act;               // [tokens][lda]: q | k | v (after prep) | beta | decay [n_heads each] | k . q [n_kv]
   float* o_raw;             // [tokens][n_heads * vdim]
   void* out;                // [tokens][ldo] compute dtype
   float* state;             // [slots][state_stride]: S^T [n_heads][vdim][dim], then the tail [taps - 1][channels]
@@ -42,11 +43,41 @@ struct DeltaRule {
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 
-// ---------------------------------------------------------------- prep: one block per token
-#define DR_PREP_THREADS 256
+// ---------------------------------------------------------------- prep: one block per (token, unit)
+// Units: the n_kv pairs of a q head and its k head (convolution, silu, two unit norms, and the pair's k . q, which
+// the recurrence needs once per token and not once per column), then the n_heads value heads (convolution, silu, and
+// the head's beta and decay).
+#define DR_PREP_THREADS 128
+__device__ __forceinline__ float dr_conv(const DeltaRule& P, const float* tail, int t, int in_step, int pos, int C,
+                                         int c) {
+  const int n = P.taps;
+  const float* w = P.conv_w + (size_t)c * n;
+  float acc = 0.f;
+  for (int i = n - 1; i >= 0; i--) {                 // oldest input first: one fixed order
+    float x = 0.f;
+    if (i <= in_step) x = P.proj[(size_t)(t - i) * P.ld + c];
+    else if (tail && pos - i >= 0) x = tail[(size_t)(n - 1 - (i - in_step)) * C + c];
+    acc = fmaf(w[n - 1 - i], x, acc);
+  }
+  return silu_f(acc);
+}
+
+__device__ __forceinline__ float dr_block_sum(float x, float* red) {         // every thread gets the sum
+  x = warp_sum(x);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();                                   // red may still be read from the call before
+  if (lane == 0) red[warp] = x;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int w = 0; w < DR_PREP_THREADS / 32; w++) total += red[w];
+  return total;
+}
+
 __global__ void __launch_bounds__(DR_PREP_THREADS) delta_prep_kernel(const DeltaRule P) {
-  extern __shared__ float dr_act[];                  // [channels]
-  const int t = blockIdx.x;
+  extern __shared__ float dr_act[];                  // [2 * dim] for a q/k pair, [vdim] for a value head
+  __shared__ float red[DR_PREP_THREADS / 32];
+  const int t = blockIdx.x, unit = blockIdx.y;
   const int D = P.dim, V = P.vdim, nqk = P.n_kv * D, C = 2 * nqk + P.n_heads * V;
   const int seq = P.token_seq[t];
   const int pos = P.token_pos[t];
@@ -56,33 +87,31 @@ __global__ void __launch_bounds__(DR_PREP_THREADS) delta_prep_kernel(const Delta
     in_step = t - P.seq_start[seq];
     tail = P.state + (size_t)P.seq_slot[seq] * P.state_stride + (size_t)P.n_heads * D * V;
   }
-  const int n = P.taps;
-  for (int c = threadIdx.x; c < C; c += DR_PREP_THREADS) {
-    const float* w = P.conv_w + (size_t)c * n;
-    float acc = 0.f;
-    for (int i = n - 1; i >= 0; i--) {               // oldest input first: one fixed order
-      float x = 0.f;
-      if (i <= in_step) x = P.proj[(size_t)(t - i) * P.ld + c];
-      else if (tail && pos - i >= 0) x = tail[(size_t)(n - 1 - (i - in_step)) * C + c];
-      acc = fmaf(w[n - 1 - i], x, acc);
-    }
-    dr_act[c] = silu_f(acc);
-  }
-  __syncthreads();
   float* out = P.act + (size_t)t * P.lda;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int hd = warp; hd < 2 * P.n_kv; hd += DR_PREP_THREADS / 32) {       // q heads, then k heads
-    const float* x = dr_act + (size_t)hd * D;
-    float ss = 0.f;
-    for (int d = lane; d < D; d += 32) ss = fmaf(x[d], x[d], ss);
-    ss = warp_sum(ss);
-    float mul = 1.0f / sqrtf(ss + 1e-6f);
-    if (hd < P.n_kv) mul *= 1.0f / sqrtf((float)D);
-    for (int d = lane; d < D; d += 32) out[(size_t)hd * D + d] = x[d] * mul;
+  if (unit < P.n_kv) {
+    const int cq = unit * D, ck = nqk + unit * D;
+    float sq = 0.f, sk = 0.f;
+    for (int d = threadIdx.x; d < D; d += DR_PREP_THREADS) {
+      const float q = dr_conv(P, tail, t, in_step, pos, C, cq + d), k = dr_conv(P, tail, t, in_step, pos, C, ck + d);
+      dr_act[d] = q; dr_act[D + d] = k;
+      sq = fmaf(q, q, sq); sk = fmaf(k, k, sk);
+    }
+    sq = dr_block_sum(sq, red);
+    sk = dr_block_sum(sk, red);
+    const float mq = 1.0f / sqrtf(sq + 1e-6f) * (1.0f / sqrtf((float)D)), mk = 1.0f / sqrtf(sk + 1e-6f);
+    float kq = 0.f;
+    for (int d = threadIdx.x; d < D; d += DR_PREP_THREADS) {               // a thread reads what it wrote itself
+      const float q = dr_act[d] * mq, k = dr_act[D + d] * mk;
+      out[cq + d] = q; out[ck + d] = k;
+      kq = fmaf(k, q, kq);
+    }
+    kq = dr_block_sum(kq, red);
+    if (threadIdx.x == 0) out[C + 2 * P.n_heads + unit] = kq;
+    return;
   }
-  for (int c = 2 * nqk + threadIdx.x; c < C; c += DR_PREP_THREADS) out[c] = dr_act[c];
-  if (threadIdx.x < P.n_heads) {
-    const int h = threadIdx.x;
+  const int h = unit - P.n_kv, cv = 2 * nqk + h * V;
+  for (int d = threadIdx.x; d < V; d += DR_PREP_THREADS) out[cv + d] = dr_conv(P, tail, t, in_step, pos, C, cv + d);
+  if (threadIdx.x == 0) {
     const float* row = P.proj + (size_t)t * P.ld;
     out[C + h] = 1.0f / (1.0f + expf(-row[C + h]));
     const float z = row[C + P.n_heads + h] + P.dt_bias[h];
@@ -93,9 +122,7 @@ __global__ void __launch_bounds__(DR_PREP_THREADS) delta_prep_kernel(const Delta
 
 // ---------------------------------------------------------------- the recurrence
 #define DR_THREADS 128
-#define DR_ROWS 16            // rows of S a thread holds
-#define DR_PITCH 20           // floats between two lanes' stretches of k and q in shared memory: 16-byte aligned, and
-                              // eight neighbouring lanes' float4 reads fall on different banks
+#define DR_ROWS 16            // rows of a column of S that a lane holds
 #define DR_MAX_CHUNK 16       // tokens staged in shared memory at a time, at most
 
 __device__ __forceinline__ void dr_copy4(float* dst_shared, const float* src) {
@@ -109,16 +136,25 @@ __device__ __forceinline__ void dr_copy16(float* dst_shared, const float* src) {
 __device__ __forceinline__ void dr_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void dr_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-// The state of a head lies in memory column by column (S^T: [vdim][dim]), so the 16 rows a thread holds are 64
-// contiguous bytes and neighbouring lanes read neighbouring stretches.
-template <int L>              // lanes per column: dim <= 16 * L
+// The state of a head lies in memory column by column (S^T: [vdim][dim]), so the ROWS rows a thread holds are
+// contiguous and neighbouring lanes read neighbouring stretches.  A column is spread over L lanes of ROWS rows each
+// (dim <= ROWS * L).  A token's step is one chain of dependent instructions (sums, shuffles, the update) that a
+// warp issues at one instruction in two to four cycles; measured at dim = vdim = 128, 16 heads, one sequence of
+// 2,048 tokens: 16 rows a lane 0.60 ms, 8 rows 0.72, 4 rows 0.77 (more warps, but two to three times the
+// instructions), and four tokens at a time with their mutual dot products formed once per group 0.76: what counts
+// is the number of instructions per token, which 16 rows a lane keep smallest.
+template <int ROWS, int L>
 __global__ void __launch_bounds__(DR_THREADS) delta_recur_kernel(const DeltaRule P) {
   constexpr int COLS = DR_THREADS / L;
-  constexpr int CHUNK = (64 / L) < DR_MAX_CHUNK ? ((64 / L) < 2 ? 2 : (64 / L)) : DR_MAX_CHUNK;
-  constexpr int KQ = L * DR_PITCH;
+  // floats between two lanes' stretches of k and q in shared memory: 16-byte aligned, and the float4 reads of eight
+  // neighbouring lanes fall on different banks
+  constexpr int PITCH = ROWS == 16 ? 20 : (ROWS == 8 ? 12 : ROWS);
+  constexpr int KQ = L * PITCH;
+  constexpr int FIT = 2048 / KQ;
+  constexpr int CHUNK = FIT < 4 ? 4 : (FIT > DR_MAX_CHUNK ? DR_MAX_CHUNK : (FIT & ~3));   // a multiple of four
   __shared__ __align__(16) float kq_s[2][CHUNK][2][KQ];
   __shared__ float v_s[2][CHUNK][COLS];
-  __shared__ float bg_s[2][CHUNK][2];
+  __shared__ float bg_s[2][CHUNK][4];                // beta, decay, k . q
   const int seq = blockIdx.z, h = blockIdx.y, tile = blockIdx.x;
   const int r0 = P.seq_start[seq], r1 = P.seq_start[seq + 1];
   if (r0 >= r1) return;
@@ -150,23 +186,26 @@ __global__ void __launch_bounds__(DR_THREADS) delta_recur_kernel(const DeltaRule
   }
 
   const int kv = h / (P.n_heads / P.n_kv);
-  float* Sg = slot + ((size_t)h * V + (live ? j : 0)) * D + part * DR_ROWS;
+  float* Sg = slot + ((size_t)h * V + (live ? j : 0)) * D + part * ROWS;
   const bool vec = D % 4 == 0 && (P.state_stride % 4) == 0 && (((uintptr_t)P.state) & 15) == 0;
-  float S[DR_ROWS];
+  float2 S[ROWS / 2];        // pairs of rows: the sums and the update run on packed pairs of floats (fma.f32x2)
 #pragma unroll
-  for (int i = 0; i < DR_ROWS; i += 4) {
-    const int d = part * DR_ROWS + i;
+  for (int i = 0; i < ROWS; i += 4) {
+    const int d = part * ROWS + i;
     if (live && vec && d + 3 < D) {
       const float4 v4 = *reinterpret_cast<const float4*>(Sg + i);
-      S[i] = v4.x; S[i + 1] = v4.y; S[i + 2] = v4.z; S[i + 3] = v4.w;
+      S[i / 2] = make_float2(v4.x, v4.y); S[i / 2 + 1] = make_float2(v4.z, v4.w);
     } else {
+      float e[4];
 #pragma unroll
-      for (int u = 0; u < 4; u++) S[i + u] = (live && d + u < D) ? Sg[i + u] : 0.f;
+      for (int u = 0; u < 4; u++) e[u] = (live && d + u < D) ? Sg[i + u] : 0.f;
+      S[i / 2] = make_float2(e[0], e[1]); S[i / 2 + 1] = make_float2(e[2], e[3]);
     }
   }
-  // the dimensions beyond dim in the staging buffers stay zero: nothing below writes them
-  for (int i = threadIdx.x; i < 2 * CHUNK * 2 * KQ; i += DR_THREADS) (&kq_s[0][0][0][0])[i] = 0.f;
-  __syncthreads();
+  if (D != ROWS * L) {       // the dimensions beyond dim in the staging buffers stay zero: nothing below writes them
+    for (int i = threadIdx.x; i < 2 * CHUNK * 2 * KQ; i += DR_THREADS) (&kq_s[0][0][0][0])[i] = 0.f;
+    __syncthreads();
+  }
 
   const bool vec_act = D % 4 == 0 && P.lda % 4 == 0 && (((uintptr_t)P.act) & 15) == 0;
   auto stage = [&](int buf, int c0) {                // ask for the tokens c0 .. of this sequence
@@ -176,12 +215,12 @@ __global__ void __launch_bounds__(DR_THREADS) delta_recur_kernel(const DeltaRule
       if (vec_act) {
         for (int d = 4 * threadIdx.x; d < 2 * D; d += 4 * DR_THREADS) {          // k, then q
           const int which = d >= D, dd = d - which * D;
-          dr_copy16(&kq_s[buf][tok][which][(dd / DR_ROWS) * DR_PITCH + dd % DR_ROWS], a + (which ? 0 : nqk) + dd);
+          dr_copy16(&kq_s[buf][tok][which][(dd / ROWS) * PITCH + dd % ROWS], a + (which ? 0 : nqk) + dd);
         }
       } else {
         for (int d = threadIdx.x; d < 2 * D; d += DR_THREADS) {
           const int which = d >= D, dd = d - which * D;
-          dr_copy4(&kq_s[buf][tok][which][(dd / DR_ROWS) * DR_PITCH + dd % DR_ROWS], a + (which ? 0 : nqk) + dd);
+          dr_copy4(&kq_s[buf][tok][which][(dd / ROWS) * PITCH + dd % ROWS], a + (which ? 0 : nqk) + dd);
         }
       }
     }
@@ -189,9 +228,11 @@ __global__ void __launch_bounds__(DR_THREADS) delta_recur_kernel(const DeltaRule
       const int tok = i / COLS, cc = i - tok * COLS, jj = tile * COLS + cc;
       if (jj < V) dr_copy4(&v_s[buf][tok][cc], P.act + (size_t)(c0 + tok) * P.lda + 2 * nqk + (size_t)h * V + jj);
     }
-    if (threadIdx.x < n_here * 2) {
-      const int tok = threadIdx.x >> 1, which = threadIdx.x & 1;                 // 0 = beta, 1 = decay
-      dr_copy4(&bg_s[buf][tok][which], P.act + (size_t)(c0 + tok) * P.lda + C + which * P.n_heads + h);
+    if (threadIdx.x < n_here * 4) {
+      const int tok = threadIdx.x >> 2, which = threadIdx.x & 3;                 // 0 = beta, 1 = decay, 2 = k . q
+      const float* a = P.act + (size_t)(c0 + tok) * P.lda + C;
+      if (which < 2) dr_copy4(&bg_s[buf][tok][which], a + which * P.n_heads + h);
+      else if (which == 2) dr_copy4(&bg_s[buf][tok][2], a + 2 * P.n_heads + kv);
     }
     dr_commit();
   };
@@ -206,52 +247,47 @@ __global__ void __launch_bounds__(DR_THREADS) delta_recur_kernel(const DeltaRule
     __syncthreads();                                 // this chunk has landed, and the other buffer is free again
     if (c0 + CHUNK < r1) stage(buf ^ 1, c0 + CHUNK);
     const int n_here = min(CHUNK, r1 - c0);
-    for (int tok = 0; tok < n_here; tok++) {
-      const float4* kk = reinterpret_cast<const float4*>(&kq_s[buf][tok][0][part * DR_PITCH]);
-      const float4* qq = reinterpret_cast<const float4*>(&kq_s[buf][tok][1][part * DR_PITCH]);
-      const float beta = bg_s[buf][tok][0], decay = bg_s[buf][tok][1], vj = v_s[buf][tok][col];
-      float4 k4[DR_ROWS / 4];
-      float sk[4] = {0.f, 0.f, 0.f, 0.f}, sq[4] = {0.f, 0.f, 0.f, 0.f}, kq[4] = {0.f, 0.f, 0.f, 0.f};
+    float* o_row = P.o_raw + (size_t)c0 * P.n_heads * V + (size_t)h * V + (live ? j : 0);
+#pragma unroll 2
+    for (int tok = 0; tok < n_here; tok++, o_row += (size_t)P.n_heads * V) {
+      const float4* kk = reinterpret_cast<const float4*>(&kq_s[buf][tok][0][part * PITCH]);
+      const float4* qq = reinterpret_cast<const float4*>(&kq_s[buf][tok][1][part * PITCH]);
+      const float beta = bg_s[buf][tok][0], decay = bg_s[buf][tok][1], kq = bg_s[buf][tok][2];
+      const float vj = v_s[buf][tok][col];
+      float2 k2[ROWS / 2];
+      float2 sk0 = make_float2(0.f, 0.f), sk1 = sk0, sq0 = sk0, sq1 = sk0;
 #pragma unroll
-      for (int i = 0; i < DR_ROWS / 4; i++) {
-        k4[i] = kk[i];
-        const float4 q4 = qq[i];
-        sk[0] = fmaf(S[4 * i], k4[i].x, sk[0]); sk[1] = fmaf(S[4 * i + 1], k4[i].y, sk[1]);
-        sk[2] = fmaf(S[4 * i + 2], k4[i].z, sk[2]); sk[3] = fmaf(S[4 * i + 3], k4[i].w, sk[3]);
-        sq[0] = fmaf(S[4 * i], q4.x, sq[0]); sq[1] = fmaf(S[4 * i + 1], q4.y, sq[1]);
-        sq[2] = fmaf(S[4 * i + 2], q4.z, sq[2]); sq[3] = fmaf(S[4 * i + 3], q4.w, sq[3]);
-        kq[0] = fmaf(k4[i].x, q4.x, kq[0]); kq[1] = fmaf(k4[i].y, q4.y, kq[1]);
-        kq[2] = fmaf(k4[i].z, q4.z, kq[2]); kq[3] = fmaf(k4[i].w, q4.w, kq[3]);
+      for (int i = 0; i < ROWS / 4; i++) {
+        const float4 k4 = kk[i], q4 = qq[i];
+        k2[2 * i] = make_float2(k4.x, k4.y); k2[2 * i + 1] = make_float2(k4.z, k4.w);
+        sk0 = __ffma2_rn(S[2 * i], k2[2 * i], sk0); sk1 = __ffma2_rn(S[2 * i + 1], k2[2 * i + 1], sk1);
+        sq0 = __ffma2_rn(S[2 * i], make_float2(q4.x, q4.y), sq0); sq1 = __ffma2_rn(S[2 * i + 1], make_float2(q4.z, q4.w), sq1);
       }
-      float a = (sk[0] + sk[1]) + (sk[2] + sk[3]), b = (sq[0] + sq[1]) + (sq[2] + sq[3]);
-      float c = (kq[0] + kq[1]) + (kq[2] + kq[3]);
+      const float2 sk = __fadd2_rn(sk0, sk1), sq = __fadd2_rn(sq0, sq1);
+      float a = sk.x + sk.y, b = sq.x + sq.y;
 #pragma unroll
       for (int o = 1; o < L; o <<= 1) {
         a += __shfl_xor_sync(0xffffffffu, a, o);
         b += __shfl_xor_sync(0xffffffffu, b, o);
-        c += __shfl_xor_sync(0xffffffffu, c, o);
       }
       const float u = beta * (vj - decay * a);
+      const float2 uu = make_float2(u, u), dd = make_float2(decay, decay);
 #pragma unroll
-      for (int i = 0; i < DR_ROWS / 4; i++) {
-        S[4 * i] = fmaf(k4[i].x, u, decay * S[4 * i]);
-        S[4 * i + 1] = fmaf(k4[i].y, u, decay * S[4 * i + 1]);
-        S[4 * i + 2] = fmaf(k4[i].z, u, decay * S[4 * i + 2]);
-        S[4 * i + 3] = fmaf(k4[i].w, u, decay * S[4 * i + 3]);
-      }
-      if (part == 0 && live) P.o_raw[(size_t)(c0 + tok) * P.n_heads * V + (size_t)h * V + j] = fmaf(c, u, decay * b);
+      for (int i = 0; i < ROWS / 2; i++) S[i] = __ffma2_rn(k2[i], uu, __fmul2_rn(dd, S[i]));
+      if (part == 0 && live) *o_row = fmaf(kq, u, decay * b);
     }
   }
   if (P.write_state && live) {
 #pragma unroll
-    for (int i = 0; i < DR_ROWS; i += 4) {
-      const int d = part * DR_ROWS + i;
+    for (int i = 0; i < ROWS; i += 4) {
+      const int d = part * ROWS + i;
+      const float e[4] = {S[i / 2].x, S[i / 2].y, S[i / 2 + 1].x, S[i / 2 + 1].y};
       if (vec && d + 3 < D) {
-        *reinterpret_cast<float4*>(Sg + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+        *reinterpret_cast<float4*>(Sg + i) = make_float4(e[0], e[1], e[2], e[3]);
       } else {
 #pragma unroll
         for (int u = 0; u < 4; u++)
-          if (d + u < D) Sg[i + u] = S[i + u];
+          if (d + u < D) Sg[i + u] = e[u];
       }
     }
   }
@@ -279,10 +315,24 @@ static int delta_check(const DeltaRule& P) {
   if (P.n_heads < 1 || P.n_kv < 1 || P.n_heads % P.n_kv != 0 || P.dim < 1 || P.vdim < 1 || P.taps < 1)
     return STRATUM_ERR_SHAPE;
   const int C = 2 * P.n_kv * P.dim + P.n_heads * P.vdim;
-  if (P.ld < C + 2 * P.n_heads + P.n_heads * P.vdim || P.lda < C + 2 * P.n_heads) return STRATUM_ERR_SHAPE;
+  if (P.ld < C + 2 * P.n_heads + P.n_heads * P.vdim || P.lda < C + 2 * P.n_heads + P.n_kv) return STRATUM_ERR_SHAPE;
   if (P.state_stride < P.n_heads * P.dim * P.vdim + (P.taps - 1) * C) return STRATUM_ERR_SHAPE;
-  if (P.n_heads > DR_PREP_THREADS || P.dim > 32 * 16) return STRATUM_ERR_LIMIT;
+  if (P.dim > 32 * DR_ROWS) return STRATUM_ERR_LIMIT;
+  if (P.n_heads > 65535 || P.n_heads + P.n_kv > 65535 || P.n_seqs > 65535) return STRATUM_ERR_LIMIT;
   return 0;
+}
+
+static int lanes_for(int rows, int dim) {
+  int L = 1;
+  while (rows * L < dim) L <<= 1;
+  return L;
+}
+
+template <int L>
+static void recur_launch(const DeltaRule& P, cudaStream_t stream) {
+  const int cols = DR_THREADS / L;
+  const dim3 grid((P.vdim + cols - 1) / cols, P.n_heads, P.n_seqs);
+  delta_recur_kernel<DR_ROWS, L><<<grid, DR_THREADS, 0, stream>>>(P);
 }
 
 // Everything of a step: prep, recurrence, finish (three launches).  out_dtype: the compute dtype of `out`.
@@ -291,28 +341,17 @@ STRATUM_EXPORT int stratum_delta_rule(const DeltaRule* params, int out_dtype, cu
   if (P.n_tokens <= 0 || P.n_seqs <= 0) return 0;
   const int bad = delta_check(P);
   if (bad) return bad;
-  const int C = 2 * P.n_kv * P.dim + P.n_heads * P.vdim;
-  const size_t smem = (size_t)C * sizeof(float);
-  if (smem > 200 * 1024) return STRATUM_ERR_LIMIT;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(delta_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
-  delta_prep_kernel<<<P.n_tokens, DR_PREP_THREADS, smem, stream>>>(P);
+  const dim3 prep_grid(P.n_tokens, P.n_kv + P.n_heads);
+  delta_prep_kernel<<<prep_grid, DR_PREP_THREADS, 2 * (size_t)P.dim * sizeof(float), stream>>>(P);
   int st = launch_status();
   if (st) return st;
-  int L = 1;
-  while (DR_ROWS * L < P.dim) L <<= 1;
-  const int cols = DR_THREADS / L;
-  if (P.n_heads > 65535 || P.n_seqs > 65535) return STRATUM_ERR_LIMIT;
-  const dim3 grid((P.vdim + cols - 1) / cols, P.n_heads, P.n_seqs);
-  switch (L) {
-    case 1: delta_recur_kernel<1><<<grid, DR_THREADS, 0, stream>>>(P); break;
-    case 2: delta_recur_kernel<2><<<grid, DR_THREADS, 0, stream>>>(P); break;
-    case 4: delta_recur_kernel<4><<<grid, DR_THREADS, 0, stream>>>(P); break;
-    case 8: delta_recur_kernel<8><<<grid, DR_THREADS, 0, stream>>>(P); break;
-    case 16: delta_recur_kernel<16><<<grid, DR_THREADS, 0, stream>>>(P); break;
-    default: delta_recur_kernel<32><<<grid, DR_THREADS, 0, stream>>>(P); break;
+  switch (lanes_for(DR_ROWS, P.dim)) {
+    case 1: recur_launch<1>(P, stream); break;
+    case 2: recur_launch<2>(P, stream); break;
+    case 4: recur_launch<4>(P, stream); break;
+    case 8: recur_launch<8>(P, stream); break;
+    case 16: recur_launch<16>(P, stream); break;
+    default: recur_launch<32>(P, stream); break;
   }
   st = launch_status();
   if (st) return st;

@@ -810,7 +810,7 @@ def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt
                n_heads: int, n_kv: int, dim: int, vdim: int, eps: float, write_state: bool) -> None:
     """One step of the gated delta rule for every sequence of the step (see csrc/delta_rule.cu).  proj float32
     [tokens, >= C + 2 n_heads + n_heads vdim] with C = 2 n_kv dim + n_heads vdim conv channels; conv_w float32
-    [C, taps]; act [tokens, >= C + 2 n_heads] and o_raw [tokens, n_heads vdim] float32 scratch; out [tokens, >=
+    [C, taps]; act [tokens, >= C + 2 n_heads + n_kv] and o_raw [tokens, n_heads vdim] float32 scratch; out [tokens, >=
     n_heads vdim] in the compute dtype; state float32 [slots, n_heads dim vdim + (taps - 1) C]."""
     for name, t in (("proj", proj), ("act", act)):
         _need(t, name, torch.float32, contiguous=False)

@@ -80,7 +80,7 @@ class GatedDeltaRule(Mixer):
         f32 = torch.float32
         proj = self.runtime.empty(T, padded(self.width), dtype=f32)
         self.w_in(xin, out=proj[:, :self.width], mode=STORE_F32)
-        act = self.runtime.empty(T, self.channels + 2 * self.n_heads, dtype=f32)
+        act = self.runtime.empty(T, padded(self.channels + 2 * self.n_heads + self.n_kv), dtype=f32)
         o_raw = self.runtime.empty(T, self.v_cols, dtype=f32)
         out = self.runtime.empty(T, padded(self.v_cols))
         K.delta_rule(proj, self.conv_w, self.a_log, self.dt_bias, self.gain, act, o_raw, out, cache.state,

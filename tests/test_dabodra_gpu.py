@@ -119,15 +119,17 @@ def test_router_kernel(experts, top, groups, keep, dtype):
 
 
 @pytest.mark.parametrize("heads,kv,dim,vdim,taps", [(4, 2, 24, 40, 3), (3, 3, 40, 16, 5), (2, 1, 64, 32, 4), (1, 1, 8, 8, 1),
-                                                    (2, 2, 130, 70, 2)])
+                                                    (2, 2, 130, 70, 2), (4, 2, 128, 36, 4), (1, 1, 260, 12, 2),
+                                                    (2, 1, 100, 24, 3)])
 def test_delta_rule_kernels(heads, kv, dim, vdim, taps):
     """The three kernels of the delta rule on projections made here: two sequences of unequal lengths whose tokens
-    come in three steps (many, two, one), states in slots that lie apart, against the plain loop over whole sequences."""
+    come in three steps (many, three and two, one), states in slots that lie apart, against the plain loop over whole
+    sequences."""
     from stratum_b200 import kernels as K
     rng = np.random.default_rng(dim + vdim)
     C = 2 * kv * dim + heads * vdim
     width = C + 2 * heads + heads * vdim
-    lens = (23, 9)
+    lens = (77, 9)
     proj = [rng.standard_normal((n, width)) for n in lens]
     conv = rng.uniform(-0.8, 0.8, (C, taps))
     a_log, dt_bias, gain = rng.uniform(-2, 0.5, heads), rng.uniform(-1, 1, heads), rng.uniform(0.5, 1.5, vdim)
@@ -144,16 +146,16 @@ def test_delta_rule_kernels(heads, kv, dim, vdim, taps):
     slots = (4, 1)
     done = [0, 0]
     got = [[], []]
-    for cut in ((20, 6), (2, 2), (1, 1)):
-        rows = np.concatenate([proj[i][done[i]:done[i] + cut[i]] for i in range(2)])
-        T = rows.shape[0]
+    for cut in ((73, 6), (3, 2), (1, 1)):
+        rows_ = np.concatenate([proj[i][done[i]:done[i] + cut[i]] for i in range(2)])
+        T = rows_.shape[0]
         pos = np.concatenate([np.arange(done[i], done[i] + cut[i]) for i in range(2)])
         seq = np.concatenate([np.full(cut[i], i) for i in range(2)])
         start = np.array([0, cut[0], T])
-        act = torch.empty(T, C + 2 * heads, device="cuda")
+        act = torch.empty(T, C + 2 * heads + kv, device="cuda")
         o_raw = torch.empty(T, heads * vdim, device="cuda")
         out = torch.empty(T, heads * vdim, device="cuda")
-        K.delta_rule(_dev(rows), _dev(conv), _dev(a_log), _dev(dt_bias), _dev(gain), act, o_raw, out, state,
+        K.delta_rule(_dev(rows_), _dev(conv), _dev(a_log), _dev(dt_bias), _dev(gain), act, o_raw, out, state,
                      _dev(pos, torch.int32), _dev(seq, torch.int32), _dev(start, torch.int32),
                      _dev(np.array(slots), torch.int32), heads, kv, dim, vdim, 1e-5, True)
         o = out.cpu().numpy()
