@@ -23,9 +23,14 @@ class RMSNorm(Norm):
         super().__init__(spec, runtime)
         self.size = int(spec["size"])
         self.eps = float(spec["eps"])
-        self.name = spec.get("tensor") or self.prefix + "weight"
+        self.tensor = spec.get("tensor")
         self.one_plus = bool(spec.get("one_plus", False))
         self.gain: Optional[torch.Tensor] = None
+
+    @property
+    def name(self) -> str:
+        """The gain's name (a part that owns this norm may move its prefix after it is made)."""
+        return self.tensor or self.prefix + "weight"
 
     def tensors(self) -> Dict[str, TensorSpec]:
         return {self.name: TensorSpec((self.size,), role="vector", init="zeros" if self.one_plus else "ones")}
