@@ -294,6 +294,15 @@ __global__ void __launch_bounds__(DR_THREADS) delta_recur_kernel(const DeltaRule
 }
 
 // ---------------------------------------------------------------- finish: one warp per (token, head)
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(bf16* p, float a, float b, float c, float d) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 v;
+  v.x = *reinterpret_cast<const uint32_t*>(&lo); v.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = v;
+}
 template <typename T>
 __global__ void __launch_bounds__(128) delta_finish_kernel(const DeltaRule P) {
   const int lane = threadIdx.x & 31;
@@ -303,12 +312,31 @@ __global__ void __launch_bounds__(128) delta_finish_kernel(const DeltaRule P) {
   const int V = P.vdim, C = 2 * P.n_kv * P.dim + P.n_heads * V;
   const float* o = P.o_raw + (size_t)t * P.n_heads * V + (size_t)h * V;
   const float* g = P.proj + (size_t)t * P.ld + C + 2 * P.n_heads + (size_t)h * V;
+  T* out = (T*)P.out + (size_t)t * P.ldo + (size_t)h * V;
+  const bool vec = V % 4 == 0 && P.ld % 4 == 0 && (C + 2 * P.n_heads) % 4 == 0 && P.ldo % 4 == 0 &&
+                   ((((uintptr_t)P.o_raw) | ((uintptr_t)P.proj) | ((uintptr_t)P.gain)) & 15) == 0 &&
+                   (((uintptr_t)P.out) & (4 * sizeof(T) - 1)) == 0;
   float ss = 0.f;
-  for (int d = lane; d < V; d += 32) ss = fmaf(o[d], o[d], ss);
+  if (vec) {
+    for (int d = 4 * lane; d < V; d += 128) {
+      const float4 x = *reinterpret_cast<const float4*>(o + d);
+      ss = fmaf(x.x, x.x, ss); ss = fmaf(x.y, x.y, ss); ss = fmaf(x.z, x.z, ss); ss = fmaf(x.w, x.w, ss);
+    }
+  } else {
+    for (int d = lane; d < V; d += 32) ss = fmaf(o[d], o[d], ss);
+  }
   ss = warp_sum(ss);
   const float mul = 1.0f / sqrtf(ss / (float)V + P.eps);
-  T* out = (T*)P.out + (size_t)t * P.ldo + (size_t)h * V;
-  for (int d = lane; d < V; d += 32) out[d] = from_float<T>(o[d] * mul * P.gain[d] * silu_f(g[d]));
+  if (vec) {
+    for (int d = 4 * lane; d < V; d += 128) {
+      const float4 x = *reinterpret_cast<const float4*>(o + d), gg = *reinterpret_cast<const float4*>(g + d);
+      const float4 w = *reinterpret_cast<const float4*>(P.gain + d);
+      store4(out + d, x.x * mul * w.x * silu_f(gg.x), x.y * mul * w.y * silu_f(gg.y), x.z * mul * w.z * silu_f(gg.z),
+             x.w * mul * w.w * silu_f(gg.w));
+    }
+  } else {
+    for (int d = lane; d < V; d += 32) out[d] = from_float<T>(o[d] * mul * P.gain[d] * silu_f(g[d]));
+  }
 }
 
 static int delta_check(const DeltaRule& P) {

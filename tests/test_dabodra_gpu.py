@@ -121,7 +121,8 @@ def test_router_kernel(experts, top, groups, keep, dtype):
 @pytest.mark.parametrize("heads,kv,dim,vdim,taps", [(4, 2, 24, 40, 3), (3, 3, 40, 16, 5), (2, 1, 64, 32, 4), (1, 1, 8, 8, 1),
                                                     (2, 2, 130, 70, 2), (4, 2, 128, 36, 4), (1, 1, 260, 12, 2),
                                                     (2, 1, 100, 24, 3)])
-def test_delta_rule_kernels(heads, kv, dim, vdim, taps):
+@pytest.mark.parametrize("long", [77, 520])
+def test_delta_rule_kernels(heads, kv, dim, vdim, taps, long):
     """The three kernels of the delta rule on projections made here: two sequences of unequal lengths whose tokens
     come in three steps (many, three and two, one), states in slots that lie apart, against the plain loop over whole
     sequences."""
@@ -129,7 +130,7 @@ def test_delta_rule_kernels(heads, kv, dim, vdim, taps):
     rng = np.random.default_rng(dim + vdim)
     C = 2 * kv * dim + heads * vdim
     width = C + 2 * heads + heads * vdim
-    lens = (77, 9)
+    lens = (long, 9)               # 520: dozens of staged token groups in the recurrence
     proj = [rng.standard_normal((n, width)) for n in lens]
     conv = rng.uniform(-0.8, 0.8, (C, taps))
     a_log, dt_bias, gain = rng.uniform(-2, 0.5, heads), rng.uniform(-1, 1, heads), rng.uniform(0.5, 1.5, vdim)
@@ -146,7 +147,7 @@ def test_delta_rule_kernels(heads, kv, dim, vdim, taps):
     slots = (4, 1)
     done = [0, 0]
     got = [[], []]
-    for cut in ((73, 6), (3, 2), (1, 1)):
+    for cut in ((long - 4, 6), (3, 2), (1, 1)):
         rows_ = np.concatenate([proj[i][done[i]:done[i] + cut[i]] for i in range(2)])
         T = rows_.shape[0]
         pos = np.concatenate([np.arange(done[i], done[i] + cut[i]) for i in range(2)])
