@@ -30,9 +30,9 @@ struct MoeRoute {
   float scale, reserved;
 };
 
-#define MR_WARPS 4
+#define MR_WARPS 8
 
-// one block per token: the warps share the experts' dot products (warp w takes experts w, w + 4, ...; a lane's partial
+// one block per token: the warps share the experts' dot products (warp w takes experts w, w + 8, ...; a lane's partial
 // sum runs over its elements in order, four at a time where the rows are aligned), then warp 0 chooses
 template <typename T>
 __global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(const MoeRoute P) {
@@ -49,9 +49,9 @@ __global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(const MoeRoute
     const float* w = P.w_router + (size_t)e * P.width;
     float acc = 0.f;
     if (vec) {
-      for (int i = lane * 4; i < P.width; i += 128) {
-        const float4 wv = *reinterpret_cast<const float4*>(w + i);
-        float x0, x1, x2, x3;
+      // four stretches of four elements in flight per lane, each with a sum of its own; the sums are added in one
+      // fixed order, which depends on the row's length alone
+      auto x4 = [&](int i, float& x0, float& x1, float& x2, float& x3) {
         if constexpr (sizeof(T) == 4) {
           const float4 xv = *reinterpret_cast<const float4*>(x + i);
           x0 = xv.x; x1 = xv.y; x2 = xv.z; x3 = xv.w;
@@ -61,8 +61,28 @@ __global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(const MoeRoute
           const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&xv.y);
           x0 = __low2float(lo); x1 = __high2float(lo); x2 = __low2float(hi); x3 = __high2float(hi);
         }
-        acc = fmaf(x0, wv.x, acc); acc = fmaf(x1, wv.y, acc); acc = fmaf(x2, wv.z, acc); acc = fmaf(x3, wv.w, acc);
+      };
+      float part[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int i0 = lane * 4; i0 < P.width; i0 += 512) {
+        float4 wv[4];
+        float xs[4][4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          const int i = i0 + 128 * u;
+          wv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          xs[u][0] = xs[u][1] = xs[u][2] = xs[u][3] = 0.f;
+          if (i < P.width) {
+            wv[u] = *reinterpret_cast<const float4*>(w + i);
+            x4(i, xs[u][0], xs[u][1], xs[u][2], xs[u][3]);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          part[u] = fmaf(xs[u][0], wv[u].x, part[u]); part[u] = fmaf(xs[u][1], wv[u].y, part[u]);
+          part[u] = fmaf(xs[u][2], wv[u].z, part[u]); part[u] = fmaf(xs[u][3], wv[u].w, part[u]);
+        }
       }
+      acc = (part[0] + part[1]) + (part[2] + part[3]);
     } else {
       for (int i = lane; i < P.width; i += 32) acc = fmaf(to_float(x[i]), w[i], acc);
     }
