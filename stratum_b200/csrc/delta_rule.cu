@@ -55,8 +55,8 @@ __device__ __forceinline__ float dr_conv(const DeltaRule& P, const float* tail, 
   float acc = 0.f;
   for (int i = n - 1; i >= 0; i--) {                 // oldest input first: one fixed order
     float x = 0.f;
-    if (i <= in_step) x = P.proj[(size_t)(t - i) * P.ld + c];
-    else if (tail && pos - i >= 0) x = tail[(size_t)(n - 1 - (i - in_step)) * C + c];
+    if (i <= in_step) x = ld_fresh(P.proj + (size_t)(t - i) * P.ld + c);
+    else if (tail && pos - i >= 0) x = ld_fresh(tail + (size_t)(n - 1 - (i - in_step)) * C + c);
     acc = fmaf(w[n - 1 - i], x, acc);
   }
   return silu_f(acc);
@@ -77,6 +77,8 @@ __device__ __forceinline__ float dr_block_sum(float x, float* red) {         // 
 __global__ void __launch_bounds__(DR_PREP_THREADS) delta_prep_kernel(const DeltaRule P) {
   extern __shared__ float dr_act[];                  // [2 * dim] for a q/k pair, [vdim] for a value head
   __shared__ float red[DR_PREP_THREADS / 32];
+  pdl_trigger();
+  pdl_wait();                // the projection and the state are the work of kernels before this one: ld_fresh
   const int t = blockIdx.x, unit = blockIdx.y;
   const int D = P.dim, V = P.vdim, nqk = P.n_kv * D, C = 2 * nqk + P.n_heads * V;
   const int seq = P.token_seq[t];
@@ -113,8 +115,8 @@ __global__ void __launch_bounds__(DR_PREP_THREADS) delta_prep_kernel(const Delta
   for (int d = threadIdx.x; d < V; d += DR_PREP_THREADS) out[cv + d] = dr_conv(P, tail, t, in_step, pos, C, cv + d);
   if (threadIdx.x == 0) {
     const float* row = P.proj + (size_t)t * P.ld;
-    out[C + h] = 1.0f / (1.0f + expf(-row[C + h]));
-    const float z = row[C + P.n_heads + h] + P.dt_bias[h];
+    out[C + h] = 1.0f / (1.0f + expf(-ld_fresh(row + C + h)));
+    const float z = ld_fresh(row + C + P.n_heads + h) + P.dt_bias[h];
     const float sp = z > 20.f ? z : log1pf(expf(z));
     out[C + P.n_heads + h] = expf(-expf(P.a_log[h]) * sp);
   }
@@ -155,6 +157,7 @@ __global__ void __launch_bounds__(DR_THREADS) delta_recur_kernel(const DeltaRule
   __shared__ __align__(16) float kq_s[2][CHUNK][2][KQ];
   __shared__ float v_s[2][CHUNK][COLS];
   __shared__ float bg_s[2][CHUNK][4];                // beta, decay, k . q
+  pdl_trigger();             // (launched the ordinary way itself: it starts when prep is done; its loads need no care)
   const int seq = blockIdx.z, h = blockIdx.y, tile = blockIdx.x;
   const int r0 = P.seq_start[seq], r1 = P.seq_start[seq + 1];
   if (r0 >= r1) return;
@@ -261,7 +264,8 @@ __global__ void __launch_bounds__(DR_THREADS) delta_recur_kernel(const DeltaRule
         const float4 k4 = kk[i], q4 = qq[i];
         k2[2 * i] = make_float2(k4.x, k4.y); k2[2 * i + 1] = make_float2(k4.z, k4.w);
         sk0 = __ffma2_rn(S[2 * i], k2[2 * i], sk0); sk1 = __ffma2_rn(S[2 * i + 1], k2[2 * i + 1], sk1);
-        sq0 = __ffma2_rn(S[2 * i], make_float2(q4.x, q4.y), sq0); sq1 = __ffma2_rn(S[2 * i + 1], make_float2(q4.z, q4.w), sq1);
+        sq0 = __ffma2_rn(S[2 * i], make_float2(q4.x, q4.y), sq0);
+        sq1 = __ffma2_rn(S[2 * i + 1], make_float2(q4.z, q4.w), sq1);
       }
       const float2 sk = __fadd2_rn(sk0, sk1), sq = __fadd2_rn(sq0, sq1);
       float a = sk.x + sk.y, b = sq.x + sq.y;
@@ -306,6 +310,8 @@ __device__ __forceinline__ void store4(bf16* p, float a, float b, float c, float
 template <typename T>
 __global__ void __launch_bounds__(128) delta_finish_kernel(const DeltaRule P) {
   const int lane = threadIdx.x & 31;
+  pdl_trigger();
+  pdl_wait();                // o_raw and the projection are the work of kernels before this one: ld_fresh
   const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (item >= (long long)P.n_tokens * P.n_heads) return;
   const int t = (int)(item / P.n_heads), h = (int)(item - (long long)t * P.n_heads);
@@ -319,23 +325,28 @@ __global__ void __launch_bounds__(128) delta_finish_kernel(const DeltaRule P) {
   float ss = 0.f;
   if (vec) {
     for (int d = 4 * lane; d < V; d += 128) {
-      const float4 x = *reinterpret_cast<const float4*>(o + d);
+      const float4 x = ld_fresh(reinterpret_cast<const float4*>(o + d));
       ss = fmaf(x.x, x.x, ss); ss = fmaf(x.y, x.y, ss); ss = fmaf(x.z, x.z, ss); ss = fmaf(x.w, x.w, ss);
     }
   } else {
-    for (int d = lane; d < V; d += 32) ss = fmaf(o[d], o[d], ss);
+    for (int d = lane; d < V; d += 32) {
+      const float x = ld_fresh(o + d);
+      ss = fmaf(x, x, ss);
+    }
   }
   ss = warp_sum(ss);
   const float mul = 1.0f / sqrtf(ss / (float)V + P.eps);
   if (vec) {
     for (int d = 4 * lane; d < V; d += 128) {
-      const float4 x = *reinterpret_cast<const float4*>(o + d), gg = *reinterpret_cast<const float4*>(g + d);
+      const float4 x = ld_fresh(reinterpret_cast<const float4*>(o + d));
+      const float4 gg = ld_fresh(reinterpret_cast<const float4*>(g + d));
       const float4 w = *reinterpret_cast<const float4*>(P.gain + d);
       store4(out + d, x.x * mul * w.x * silu_f(gg.x), x.y * mul * w.y * silu_f(gg.y), x.z * mul * w.z * silu_f(gg.z),
              x.w * mul * w.w * silu_f(gg.w));
     }
   } else {
-    for (int d = lane; d < V; d += 32) out[d] = from_float<T>(o[d] * mul * P.gain[d] * silu_f(g[d]));
+    for (int d = lane; d < V; d += 32)
+      out[d] = from_float<T>(ld_fresh(o + d) * mul * P.gain[d] * silu_f(ld_fresh(g + d)));
   }
 }
 
@@ -370,7 +381,7 @@ STRATUM_EXPORT int stratum_delta_rule(const DeltaRule* params, int out_dtype, cu
   const int bad = delta_check(P);
   if (bad) return bad;
   const dim3 prep_grid(P.n_tokens, P.n_kv + P.n_heads);
-  delta_prep_kernel<<<prep_grid, DR_PREP_THREADS, 2 * (size_t)P.dim * sizeof(float), stream>>>(P);
+  launch_pdl(delta_prep_kernel, prep_grid, DR_PREP_THREADS, 2 * (size_t)P.dim * sizeof(float), stream, P);
   int st = launch_status();
   if (st) return st;
   switch (lanes_for(DR_ROWS, P.dim)) {
@@ -386,8 +397,8 @@ STRATUM_EXPORT int stratum_delta_rule(const DeltaRule* params, int out_dtype, cu
   const long long items = (long long)P.n_tokens * P.n_heads;
   const long long blocks = (items + 3) / 4;
   if (blocks > 0x7fffffffLL) return STRATUM_ERR_LIMIT;
-  if (out_dtype == STRATUM_DT_F32) delta_finish_kernel<float><<<(unsigned)blocks, 128, 0, stream>>>(P);
-  else if (out_dtype == STRATUM_DT_BF16) delta_finish_kernel<bf16><<<(unsigned)blocks, 128, 0, stream>>>(P);
+  if (out_dtype == STRATUM_DT_F32) launch_pdl(delta_finish_kernel<float>, (unsigned)blocks, 128, 0, stream, P);
+  else if (out_dtype == STRATUM_DT_BF16) launch_pdl(delta_finish_kernel<bf16>, (unsigned)blocks, 128, 0, stream, P);
   else return STRATUM_ERR_DTYPE;
   return launch_status();
 }

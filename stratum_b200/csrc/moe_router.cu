@@ -38,6 +38,8 @@ template <typename T>
 __global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(const MoeRoute P) {
   extern __shared__ float mr_s[];                    // s [E], c [E], group score [n_groups]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_trigger();
+  pdl_wait();                                        // x is the work of a kernel before this one: ld_fresh
   const int t = blockIdx.x;
   const int E = P.n_experts, G = P.n_groups, per = E / G;
   float* s = mr_s;
@@ -53,10 +55,10 @@ __global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(const MoeRoute
       // fixed order, which depends on the row's length alone
       auto x4 = [&](int i, float& x0, float& x1, float& x2, float& x3) {
         if constexpr (sizeof(T) == 4) {
-          const float4 xv = *reinterpret_cast<const float4*>(x + i);
+          const float4 xv = ld_fresh(reinterpret_cast<const float4*>(x + i));
           x0 = xv.x; x1 = xv.y; x2 = xv.z; x3 = xv.w;
         } else {
-          const uint2 xv = *reinterpret_cast<const uint2*>(x + i);
+          const uint2 xv = __ldcg(reinterpret_cast<const uint2*>(x + i));
           const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&xv.x);
           const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&xv.y);
           x0 = __low2float(lo); x1 = __high2float(lo); x2 = __low2float(hi); x3 = __high2float(hi);
@@ -84,7 +86,7 @@ __global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(const MoeRoute
       }
       acc = (part[0] + part[1]) + (part[2] + part[3]);
     } else {
-      for (int i = lane; i < P.width; i += 32) acc = fmaf(to_float(x[i]), w[i], acc);
+      for (int i = lane; i < P.width; i += 32) acc = fmaf(ld_fresh(x + i), w[i], acc);
     }
     acc = warp_sum(acc);
     if (lane == 0) {
@@ -155,8 +157,8 @@ STRATUM_EXPORT int stratum_moe_route(const MoeRoute* params, int dtype, cudaStre
   const size_t smem = (size_t)(2 * P.n_experts + P.n_groups) * sizeof(float);
   if (smem > 48 * 1024) return STRATUM_ERR_LIMIT;
   const int blocks = P.n_tokens;
-  if (dtype == STRATUM_DT_F32) moe_route_kernel<float><<<blocks, MR_WARPS * 32, smem, stream>>>(P);
-  else if (dtype == STRATUM_DT_BF16) moe_route_kernel<bf16><<<blocks, MR_WARPS * 32, smem, stream>>>(P);
+  if (dtype == STRATUM_DT_F32) launch_pdl(moe_route_kernel<float>, blocks, MR_WARPS * 32, smem, stream, P);
+  else if (dtype == STRATUM_DT_BF16) launch_pdl(moe_route_kernel<bf16>, blocks, MR_WARPS * 32, smem, stream, P);
   else return STRATUM_ERR_DTYPE;
   return launch_status();
 }
@@ -164,8 +166,10 @@ STRATUM_EXPORT int stratum_moe_route(const MoeRoute* params, int dtype, cudaStre
 // a thread takes eight neighbouring columns of one row (they lie in one expert's stretch when `block` is a multiple
 // of eight; otherwise, and for rows that are not 16-byte aligned, column by column)
 template <typename T>
-__global__ void scale_column_blocks_kernel(T* a, int lda, const float* __restrict__ w, int ldw, int n_rows, int block,
-                                           int n_blocks, int vec) {
+__global__ void scale_column_blocks_kernel(T* a, int lda, const float* w, int ldw, int n_rows, int block, int n_blocks,
+                                           int vec) {
+  pdl_trigger();
+  pdl_wait();                                        // a and w are the work of kernels before this one: ld_fresh
   const int cols = block * n_blocks;
   const int per_row = (cols + 7) / 8;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -174,22 +178,23 @@ __global__ void scale_column_blocks_kernel(T* a, int lda, const float* __restric
   T* p = a + (size_t)r * lda + c0;
   const float* wr = w + (size_t)r * ldw;
   if (vec && c0 + 8 <= cols) {
-    const float f = wr[c0 / block];
+    const float f = ld_fresh(wr + c0 / block);
     if constexpr (sizeof(T) == 2) {
-      uint4 v = *reinterpret_cast<uint4*>(p);
+      uint4 v = ld_fresh(reinterpret_cast<const uint4*>(p));
       __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
 #pragma unroll
       for (int u = 0; u < 4; u++) h[u] = __floats2bfloat162_rn(__low2float(h[u]) * f, __high2float(h[u]) * f);
       *reinterpret_cast<uint4*>(p) = v;
     } else {
       float4* q = reinterpret_cast<float4*>(p);
-      float4 x = q[0], y = q[1];
+      float4 x = ld_fresh(q), y = ld_fresh(q + 1);
       q[0] = make_float4(x.x * f, x.y * f, x.z * f, x.w * f);
       q[1] = make_float4(y.x * f, y.y * f, y.z * f, y.w * f);
     }
     return;
   }
-  for (int c = c0; c < min(c0 + 8, cols); c++) p[c - c0] = from_float<T>(to_float(p[c - c0]) * wr[c / block]);
+  for (int c = c0; c < min(c0 + 8, cols); c++)
+    p[c - c0] = from_float<T>(ld_fresh((const T*)p + (c - c0)) * ld_fresh(wr + c / block));
 }
 
 STRATUM_EXPORT int stratum_scale_column_blocks(void* a, int dtype, int lda, const float* w, int ldw, int n_rows,
@@ -202,9 +207,11 @@ STRATUM_EXPORT int stratum_scale_column_blocks(void* a, int dtype, int lda, cons
   const int elem = dtype == STRATUM_DT_F32 ? 4 : 2;
   const int vec = block % 8 == 0 && ((size_t)lda * elem) % 16 == 0 && ((uintptr_t)a & 15) == 0;
   if (dtype == STRATUM_DT_F32)
-    scale_column_blocks_kernel<float><<<(unsigned)blocks, 256, 0, stream>>>((float*)a, lda, w, ldw, n_rows, block, n_blocks, vec);
+    launch_pdl(scale_column_blocks_kernel<float>, (unsigned)blocks, 256, 0, stream, (float*)a, lda, w, ldw, n_rows,
+               block, n_blocks, vec);
   else if (dtype == STRATUM_DT_BF16)
-    scale_column_blocks_kernel<bf16><<<(unsigned)blocks, 256, 0, stream>>>((bf16*)a, lda, w, ldw, n_rows, block, n_blocks, vec);
+    launch_pdl(scale_column_blocks_kernel<bf16>, (unsigned)blocks, 256, 0, stream, (bf16*)a, lda, w, ldw, n_rows, block,
+               n_blocks, vec);
   else return STRATUM_ERR_DTYPE;
   return launch_status();
 }

@@ -36,12 +36,20 @@ struct QKNormRope {
 template <typename T>
 __global__ void __launch_bounds__(QK_THREADS) qk_norm_rope_kernel(const QKNormRope P) {
   __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();                                        // the projection is the work of the kernel before: ld_fresh
   const int t = blockIdx.x;
   const float* row = P.proj + (size_t)t * P.ld;
   const int D = P.dim, nq = P.n_heads * D, nk = P.n_kv * D;
   float ssq = 0.f, ssk = 0.f;
-  for (int c = threadIdx.x; c < nq; c += QK_THREADS) ssq = fmaf(row[c], row[c], ssq);
-  for (int c = threadIdx.x; c < nk; c += QK_THREADS) ssk = fmaf(row[nq + c], row[nq + c], ssk);
+  for (int c = threadIdx.x; c < nq; c += QK_THREADS) {
+    const float v = ld_fresh(row + c);
+    ssq = fmaf(v, v, ssq);
+  }
+  for (int c = threadIdx.x; c < nk; c += QK_THREADS) {
+    const float v = ld_fresh(row + nq + c);
+    ssk = fmaf(v, v, ssk);
+  }
   ssq = block_sum(ssq, scratch);
   ssk = block_sum(ssk, scratch);
   const float sq = 1.0f / sqrtf(ssq / (float)nq + P.eps), sk = 1.0f / sqrtf(ssk / (float)nk + P.eps);
@@ -51,10 +59,10 @@ __global__ void __launch_bounds__(QK_THREADS) qk_norm_rope_kernel(const QKNormRo
   T* qo = (T*)P.q_out + (size_t)t * P.ldq;
   for (int c = threadIdx.x; c < nq; c += QK_THREADS) {
     const int d = c % D;
-    float v = row[c] * sq * P.q_gain[c];
+    float v = ld_fresh(row + c) * sq * P.q_gain[c];
     if (d < rot) {
       const int mate = (d & 1) ? c - 1 : c + 1;
-      const float w = row[mate] * sq * P.q_gain[mate];
+      const float w = ld_fresh(row + mate) * sq * P.q_gain[mate];
       float sn, cs;
       sincosf((float)pos * P.inv_freq[d >> 1], &sn, &cs);
       v = (d & 1) ? v * cs + w * sn : v * cs - w * sn;
@@ -68,12 +76,12 @@ __global__ void __launch_bounds__(QK_THREADS) qk_norm_rope_kernel(const QKNormRo
   for (int c = threadIdx.x; c < nk; c += QK_THREADS) {
     const int h = c / D, d = c - h * D;
     const size_t at = (((size_t)page * P.n_kv + h) * P.page_tokens + in_page) * D + d;
-    const float raw = row[nq + c];
+    const float raw = ld_fresh(row + nq + c);
     ((T*)P.v_cache)[at] = from_float<T>(raw);
     float v = raw * sk * P.k_gain[c];
     if (d < rot) {
       const int mate = (d & 1) ? c - 1 : c + 1;
-      const float w = row[nq + mate] * sk * P.k_gain[mate];
+      const float w = ld_fresh(row + nq + mate) * sk * P.k_gain[mate];
       float sn, cs;
       sincosf((float)pos * P.inv_freq[d >> 1], &sn, &cs);
       v = (d & 1) ? v * cs + w * sn : v * cs - w * sn;
@@ -88,8 +96,8 @@ STRATUM_EXPORT int stratum_qk_norm_rope(const QKNormRope* params, int dtype, cud
   if (P.n_heads < 1 || P.n_kv < 1 || P.dim < 1 || P.rot_pairs < 0 || 2 * P.rot_pairs > P.dim || P.page_tokens < 1)
     return STRATUM_ERR_SHAPE;
   if (P.ld < (P.n_heads + P.n_kv) * P.dim || P.ldq < P.n_heads * P.dim) return STRATUM_ERR_SHAPE;
-  if (dtype == STRATUM_DT_F32) qk_norm_rope_kernel<float><<<P.n_tokens, QK_THREADS, 0, stream>>>(P);
-  else if (dtype == STRATUM_DT_BF16) qk_norm_rope_kernel<bf16><<<P.n_tokens, QK_THREADS, 0, stream>>>(P);
+  if (dtype == STRATUM_DT_F32) launch_pdl(qk_norm_rope_kernel<float>, P.n_tokens, QK_THREADS, 0, stream, P);
+  else if (dtype == STRATUM_DT_BF16) launch_pdl(qk_norm_rope_kernel<bf16>, P.n_tokens, QK_THREADS, 0, stream, P);
   else return STRATUM_ERR_DTYPE;
   return launch_status();
 }
