@@ -311,6 +311,28 @@ def test_prefill_against_token_by_token(setup):
         assert np.max(np.abs(whole - single)) <= 2e-5 * np.max(np.abs(ref))
 
 
+def test_the_same_bits_every_run(setup):
+    """A batch of prompts and some decoded tokens, three times over in slots, pages and state rows that were just given
+    back: every run's logits are the same bits (the small kernels begin while the kernel before them still runs; a
+    value read too early, or a sum whose order depends on timing, would show here)."""
+    from stratum_b200.engine import StepEntry
+    name, dtype, cfg, w, engine, _ = setup
+    rng = np.random.default_rng(17)
+    prompts = [[int(t) for t in rng.integers(0, cfg["vocab"], n)] for n in (90, 7, 64, 33)]
+    more = [[int(t) for t in rng.integers(0, cfg["vocab"], 6)] for _ in prompts]
+    runs = []
+    for _ in range(3):
+        slots = [engine.acquire() for _ in prompts]
+        got = [engine.step([StepEntry(s, p, list(range(len(p)))) for s, p in zip(slots, prompts)]).cpu().numpy()]
+        for i in range(6):
+            got.append(engine.step([StepEntry(s, [m[i]], [0]) for s, m in zip(slots, more)]).cpu().numpy())
+        for s in slots:
+            engine.release(s)
+        runs.append(np.concatenate(got))
+    assert np.isfinite(runs[0]).all()
+    assert np.array_equal(runs[0], runs[1]) and np.array_equal(runs[0], runs[2]), f"{name} {dtype}: runs differ"
+
+
 @pytest.mark.parametrize("portion", [2, 3, 31, 64, 100])
 def test_prompt_in_portions(setup, portion):
     """A prompt cut into portions of a few sizes, down to two tokens (fewer than the convolutions' taps); portions
