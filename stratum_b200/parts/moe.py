@@ -40,7 +40,8 @@ from .spec import TensorSpec
 
 
 # rows an expert gets on average from which a prompt step takes the grouped way (T * top / experts); measured on layer
-# sizes of a 1B-like and an 8B-like model (numbers at `grouped` below).  STRATUM_MOE_GROUPED_MIN_ROWS sets it (measurements).
+# sizes of a 1B-like and an 8B-like model (numbers at `grouped` below).  STRATUM_MOE_GROUPED_MIN_ROWS sets it
+# (measurements).
 GROUPED_MIN_ROWS = int(os.environ.get("STRATUM_MOE_GROUPED_MIN_ROWS", 96))
 
 
